@@ -1,0 +1,150 @@
+/*
+ * C ABI of libfa_sm100.so: flash-attention forward and backward for NVIDIA B200
+ * (sm_100a), with an optional (B,H,M,N) additive bias / bool mask and a bias
+ * gradient written at full size.
+ *
+ * Every entry point takes plain pointers and sizes, enqueues work on the CUDA
+ * stream it is given, never synchronises the device (except where noted), never
+ * throws and never frees caller memory.  All tensors are owned by the caller.
+ * A return value of 0 means "enqueued"; any other value is an fa_error code
+ * (fa_status_string() turns it into text).
+ *
+ * The entry points replace, one for one, the host launchers of the reference
+ * project's flash_attention.py (cited per function below as FA:<line>).
+ */
+#ifndef FA_SM100_H_
+#define FA_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_ABI_VERSION 1
+
+enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 };
+
+/* What the `bias` pointer holds. */
+enum fa_bias_kind {
+  FA_BIAS_NONE = 0,
+  FA_BIAS_SAME = 1, /* float bias in the same 16-bit dtype as q; added to q.k^T*scale      */
+  FA_BIAS_BOOL = 2, /* one byte per element; 0 masks the score out, non-zero keeps it      */
+  FA_BIAS_F32 = 3   /* fp32 bias with 16-bit q/k/v (bias gradient, when asked for, is fp32) */
+};
+
+enum fa_error {
+  FA_OK = 0,
+  FA_ERR_ABI = 1,         /* struct_size does not match this library            */
+  FA_ERR_NULL = 2,        /* a required pointer is null                         */
+  FA_ERR_SHAPE = 3,       /* a dimension is < 1 or the head dim is unsupported  */
+  FA_ERR_DTYPE = 4,       /* unknown dtype / bias kind, or unsupported mix      */
+  FA_ERR_ALIGN = 5,       /* a base pointer or stride breaks the 16-byte rule   */
+  FA_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed                  */
+  FA_ERR_DEVICE_WAIT = 7, /* a kernel gave up a bounded wait (see fa_last_device_status) */
+  FA_ERR_UNSUPPORTED = 8, /* legal in the reference, not built in this library  */
+  FA_ERR_TOO_LARGE = 9    /* a size exceeds a stated limit of the entry point   */
+};
+
+/*
+ * One attention problem.  Layouts (element strides; the innermost stride of
+ * every tensor must be 1):
+ *   q, o, do, dq : (B, M, H, D)  strides {B, M, H}
+ *   k, v, dk, dv : (B, N, H, D)  strides {B, N, H}
+ *   bias, dbias  : (B, H, M, N)  strides {B, H, M}; a stride of 0 (an expanded
+ *                  view) is accepted for B and H of `bias`
+ *   lse, delta   : (B, H, M) fp32, contiguous
+ * Alignment: q/k/v/do base pointers and strides*2 bytes are multiples of 16; the
+ * same holds for bias/dbias strides in bytes (the Python layer pads when a row
+ * pitch does not qualify).
+ */
+typedef struct fa_params {
+  uint32_t struct_size; /* sizeof(fa_params), checked against the library */
+  int32_t device;       /* CUDA device ordinal all pointers live on       */
+  int32_t B, H, M, N, D;
+  int32_t dtype;       /* fa_dtype of q, k, v, o, do, dq, dk, dv          */
+  int32_t bias_kind;   /* fa_bias_kind                                    */
+  int32_t causal;      /* 1: key n is visible to query m iff n <= m       */
+  int32_t write_dbias; /* backward only: 1 = store dS into dbias          */
+  float sm_scale;      /* multiplies q.k^T (not the bias)                 */
+
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;         /* forward: out; backward: in                          */
+  const void* d_o; /* backward in: gradient of o                          */
+  void* dq;
+  void* dk;
+  void* dv;
+  const void* bias;
+  void* dbias;
+  float* lse;   /* forward out / backward in: log2-domain log-sum-exp      */
+  float* delta; /* backward scratch: rowsum(o * do), written by fa_bwd_pre */
+
+  int64_t q_stride[3];
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int64_t do_stride[3];
+  int64_t dq_stride[3];
+  int64_t dk_stride[3];
+  int64_t dv_stride[3];
+  int64_t bias_stride[3];
+  int64_t dbias_stride[3];
+} fa_params;
+
+/* Library / ABI version (FA_ABI_VERSION of the build). */
+int fa_version(void);
+
+/* Text for an fa_error code; never null. */
+const char* fa_status_string(int code);
+
+/*
+ * Forward: o = softmax(q.k^T * sm_scale + bias, masks) . v and the log2-domain
+ * log-sum-exp of every row.  Replaces _flash_attn_fwd (FA:649-685) and the
+ * _attn_fwd kernel (FA:88-194); the eager `bias * log2(e)` copy of FA:661-663 is
+ * folded into the kernel.
+ */
+int fa_fwd(const fa_params* p, void* stream);
+
+/*
+ * Backward, all three stages in order on `stream`.  Replaces _flash_attn_bwd
+ * (FA:688-763): the eager pre-scaled copies of k and bias (FA:699-704) and the
+ * zero fill of dbias (FA:799) are folded into the kernels.
+ */
+int fa_bwd(const fa_params* p, void* stream);
+
+/* The three backward stages on their own (per-kernel timing and tests). */
+int fa_bwd_pre(const fa_params* p, void* stream);  /* _attn_bwd_preprocess FA:197-233 */
+int fa_bwd_dkdv(const fa_params* p, void* stream); /* _attn_bwd_dkdv       FA:330-454 */
+int fa_bwd_dq(const fa_params* p, void* stream);   /* _attn_bwd_dq         FA:538-646 */
+
+/*
+ * Reads the device-side status word of `device` into out[0..7] (synchronises the
+ * device).  out[0] != 0 means a kernel abandoned a bounded wait; out[1..5] hold
+ * kernel id, block x, block y, wait site and loop iteration.  Returns FA_OK or
+ * FA_ERR_DEVICE_WAIT / FA_ERR_CUDA.  No counterpart in the reference.
+ */
+int fa_last_device_status(int device, int32_t out[8]);
+
+/* Clears the status word of `device` (synchronises the device). */
+int fa_reset_device_status(int device);
+
+/*
+ * Self-test of the tensor-core building blocks on one 128x128x128 tile:
+ *   mode 0: c = a . b^T            (both operands K-major in shared memory)
+ *   mode 1: c = a . b              (b MN-major)
+ *   mode 2: c = a^T . b            (both MN-major)
+ *   mode 3: c = a . b              (a staged through tensor memory, b MN-major)
+ *   mode 4: c16 = a                (shared-memory rewrite + bulk tensor store, 16-bit out)
+ * a, b: [128][128] 16-bit row-major device buffers of `dtype`; c: [128][128] fp32
+ * (mode 4: 16-bit).  Used by the test-suite to pin descriptor encodings; no
+ * counterpart in the reference.
+ */
+int fa_selftest_umma(int mode, int dtype, const void* a, const void* b, void* c, int device,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_SM100_H_ */
