@@ -1,0 +1,168 @@
+"""GPU parity: the CUDA path (through the Python API and the C ABI) against the
+fp32 oracle on identical seeded inputs.  Tolerances are the ones the target states:
+max-abs <= 2e-2 for bf16 and <= 5e-3 for fp16 (tests/_util.py: TOL)."""
+import pytest
+import torch
+
+from tests._util import check_case, make_inputs, run_ours
+from oracle import eager_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+BF, HF = torch.bfloat16, torch.float16
+
+
+def test_umma_selftest(device_ok):
+    """Descriptor encodings of every operand arrangement the kernels use."""
+    from triton_flashattn_b200 import _cabi
+
+    lib = _cabi.load()
+    for dt, code in ((BF, 1), (HF, 0)):
+        a = torch.randn(128, 128, device="cuda").to(dt)
+        b = torch.randn(128, 128, device="cuda").to(dt)
+        af, bf = a.double(), b.double()
+        refs = {0: af @ bf.T, 1: af @ bf, 2: af.T @ bf, 3: af @ bf}
+        for mode in range(5):
+            c = torch.zeros(128, 128, device="cuda", dtype=torch.float32)
+            _cabi.check(lib.fa_selftest_umma(mode, code, a.data_ptr(), b.data_ptr(), c.data_ptr(), 0, None),
+                        "fa_selftest_umma")
+            torch.cuda.synchronize()
+            if mode == 4:
+                got = c.view(dt)[:64].reshape(128, 128)
+                assert torch.equal(got, a)
+            else:
+                assert (c.double() - refs[mode]).abs().max().item() < 1e-3
+
+
+def test_config1_fp16_float_bias(device_ok):
+    # B=2, M=N=128, H=4, D=64, fp16, trainable float bias, seed 0
+    check_case(2, 128, 128, 4, 64, HF, "float", False, seed=0, sm_scale=1 / 8)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [BF, HF])
+@pytest.mark.parametrize("bias_kind,causal", [(None, False), (None, True), ("float", False),
+                                              ("float", True), ("bool", False), ("bool", True)])
+def test_small_grid(D, dtype, bias_kind, causal, device_ok):
+    check_case(2, 256, 256, 2, D, dtype, bias_kind, causal, seed=1)
+
+
+@pytest.mark.parametrize("M,N,causal", [(50, 70, False), (200, 136, False), (200, 200, True),
+                                        (128, 384, False), (384, 128, False), (100, 300, True),
+                                        (300, 100, True), (1, 1, False), (129, 1, False)])
+@pytest.mark.parametrize("bias_kind", [None, "float", "bool"])
+def test_ragged_lengths(M, N, causal, bias_kind, device_ok):
+    check_case(1, M, N, 2, 64, HF, bias_kind, causal, seed=2)
+
+
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("bias_kind", [None, "float"])
+def test_small_head_dims(D, bias_kind, device_ok):
+    check_case(1, 192, 160, 2, D, HF, bias_kind, True, seed=3)
+
+
+def test_longer_sequence_bf16(device_ok):
+    check_case(1, 1024, 1024, 2, 128, BF, "float", False, seed=4, bias_scale=0.5)
+    check_case(1, 1024, 1024, 2, 64, BF, None, True, seed=5)
+
+
+def test_non_trainable_float_bias(device_ok):
+    check_case(1, 256, 256, 2, 128, BF, "float", True, seed=6, trainable_bias=False)
+
+
+def test_dq_both_variants_agree(device_ok, monkeypatch):
+    """The streamed-dS dQ kernel and the recompute dQ kernel give the same dQ."""
+    import ctypes
+    from triton_flashattn_b200 import flash_attention as fa_mod, _cabi
+
+    q, k, v, bias, do = make_inputs(1, 384, 320, 2, 128, BF, "float", 7)
+    res = run_ours(q, k, v, bias, True, None, do)  # streamed-dS variant (trainable bias)
+    res2 = run_ours(q, k, v, bias, True, None, do, trainable_bias=False)  # recompute variant
+    assert (res["dq"].float() - res2["dq"].float()).abs().max().item() <= 2e-2
+    assert (res["dk"].float() - res2["dk"].float()).abs().max().item() == 0.0
+
+
+def test_packed_qkv_bool_causal(device_ok):
+    from triton_flashattn_b200 import flash_attention_qkvpacked_fn
+
+    B, S, H, D = 2, 384, 2, 128
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(B, S, 3, H, D, generator=g).to(BF).cuda().requires_grad_()
+    mask = torch.rand(B, H, S, S, generator=g) < 0.9
+    i = torch.arange(S)
+    mask[:, :, i, i] = True
+    mask = mask.cuda()
+    do = torch.randn(B, S, H, D, generator=g).to(BF).cuda()
+    out = flash_attention_qkvpacked_fn(qkv, mask, True, None)
+    out.backward(do)
+    q, k, v = qkv.detach()[:, :, 0], qkv.detach()[:, :, 1], qkv.detach()[:, :, 2]
+    ref = oracle.attention_backward(q, k, v, mask, True, None, do)
+    assert out.shape == (B, S, H, D) and qkv.grad.shape == qkv.shape
+    assert (out.float() - ref["out"]).abs().max().item() <= 2e-2
+    for i, name in enumerate(("dq", "dk", "dv")):
+        e = (qkv.grad[:, :, i].float() - ref[name]).abs().max().item()
+        print(name, e)
+        assert e <= 2e-2, name
+
+
+def test_expanded_bias_and_fp32_bias(device_ok):
+    from triton_flashattn_b200 import flash_attention_fn
+
+    B, M, N, H, D = 2, 128, 256, 2, 64
+    q, k, v, _, do = make_inputs(B, M, N, H, D, HF, None, 9)
+    b0 = torch.randn(1, 1, M, N, device="cuda", dtype=HF, requires_grad=True)
+    qq = q.clone().requires_grad_()
+    out = flash_attention_fn(qq, k, v, b0.expand(B, H, M, N), False, None)
+    out.backward(do)
+    ref = oracle.attention_backward(q, k, v, b0.detach().expand(B, H, M, N), False, None, do)
+    assert (out.float() - ref["out"]).abs().max().item() <= 5e-3
+    assert b0.grad.shape == b0.shape
+    assert (b0.grad.float() - ref["dbias"].sum((0, 1), keepdim=True)).abs().max().item() <= 2e-2
+    # fp32 bias with fp16 q: gradient comes back in fp32
+    b32 = torch.randn(B, H, M, N, device="cuda", requires_grad=True)
+    out = flash_attention_fn(q, k, v, b32, False, 0.3)
+    out.backward(do)
+    ref = oracle.attention_backward(q, k, v, b32.detach(), False, 0.3, do)
+    assert b32.grad.dtype == torch.float32
+    assert (out.float() - ref["out"]).abs().max().item() <= 5e-3
+    assert (b32.grad - ref["dbias"]).abs().max().item() <= 5e-3
+
+
+def test_fully_masked_row_is_zero_not_nan(device_ok):
+    q, k, v, _, do = make_inputs(1, 128, 128, 1, 64, HF, None, 10)
+    mask = torch.ones(1, 1, 128, 128, dtype=torch.bool, device="cuda")
+    mask[0, 0, 5, :] = False
+    res = run_ours(q, k, v, mask, False, None, do)
+    assert torch.all(res["out"][0, 5, 0] == 0)
+    for t in res.values():
+        assert torch.isfinite(t.float()).all()
+    ref = oracle.attention_backward(q, k, v, mask, False, None, do)
+    assert (res["out"].float() - ref["out"]).abs().max().item() <= 5e-3
+    assert (res["dq"].float() - ref["dq"]).abs().max().item() <= 5e-3
+
+
+def test_deterministic_bitwise(device_ok):
+    q, k, v, bias, do = make_inputs(2, 384, 384, 2, 128, BF, "float", 11)
+    a = run_ours(q, k, v, bias, True, None, do)
+    b = run_ours(q, k, v, bias, True, None, do)
+    for name in a:
+        assert torch.equal(a[name], b[name]), name
+
+
+def test_causal_dbias_upper_triangle_is_zero(device_ok):
+    q, k, v, bias, do = make_inputs(1, 384, 384, 1, 64, HF, "float", 12)
+    res = run_ours(q, k, v, bias, True, None, do)
+    assert torch.all(res["dbias"][0, 0].triu(1) == 0)
+
+
+def test_bad_arguments_raise():
+    from triton_flashattn_b200 import flash_attention_fn
+
+    q = torch.randn(1, 64, 2, 64, device="cuda", dtype=HF)
+    with pytest.raises(ValueError):
+        flash_attention_fn(q, q, q, torch.zeros(1, 1, 64, 64, device="cuda", dtype=HF))
+    with pytest.raises(AssertionError):
+        x = torch.randn(1, 64, 2, 48, device="cuda", dtype=HF)
+        flash_attention_fn(x, x, x)
+    with pytest.raises(TypeError):
+        flash_attention_fn(q.float(), q.float(), q.float())

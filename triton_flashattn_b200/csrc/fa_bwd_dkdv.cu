@@ -1,0 +1,526 @@
+// dK / dV (and dbias) kernel for sm_100a.
+//
+// One CTA owns 128 keys of one (batch, head) and walks the query blocks of 128
+// rows (only those at or below the diagonal when causal).  Roles (320 threads):
+//   warps 0-7  "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
+//              (query rows of the block) and on the 64-key column half (w>>2)
+//   warp 8     TMA producer (one lane): K, V once; Q ring (2), dO ring
+//   warp 9     MMA issuer (one lane), tensor-memory owner, bulk stores of dbias
+// Per query block t:
+//   S  = Q_t K^T            (tensor memory, 128 columns)
+//   dP = dO_t V^T           (tensor memory, 128 columns)
+//   row threads: P = exp2(S*scale*log2e + bias*log2e - LSE2) -> 16-bit tile sP
+//                dS = P * (dP - delta)                        -> 16-bit tile sDS
+//   dV += P^T dO_t          (sP and dO_t consumed MN-major)
+//   dK += dS^T Q_t          (sDS and Q_t consumed MN-major)
+//   dbias[b,h,m-block,n-block] <- sDS  (one bulk tensor store of the same tile)
+// The bias never touches shared memory: every row thread fetches its own 128
+// contiguous bytes (64 keys) with 128-bit loads one query block ahead.
+// Causally skipped tiles of dbias are written as zeros by this kernel, so dbias
+// needs no prior fill.
+//
+// Replaces _attn_bwd_dkdv / _attn_bwd_dkdv_inner of the reference
+// (flash_attention.py 237-454): same P, dS, dbias = dS, dK scaled by sm_scale.
+#include "fa_common.cuh"
+#include "fa_host.cuh"
+
+namespace fa {
+namespace {
+
+struct DkdvParams {
+  CUtensorMap map_q;
+  CUtensorMap map_k;
+  CUtensorMap map_v;
+  CUtensorMap map_do;
+  CUtensorMap map_dbias;
+  const void* bias;
+  void* dk;
+  void* dv;
+  const float* lse;
+  const float* delta;
+  int* status;
+  int64_t bias_sB, bias_sH, bias_sM;
+  int64_t dk_sB, dk_sN, dk_sH, dv_sB, dv_sN, dv_sH;
+  int H, M, N, D;
+  int causal, write_dbias;
+  float scale_log2;  // sm_scale * log2(e)
+  float sm_scale;
+};
+
+enum DkdvSite { kSiteKV = 1, kSiteQFull, kSiteQEmpty, kSiteDoFull, kSiteDoEmpty, kSiteSFull,
+                kSiteDpFull, kSitePReady, kSiteDsReady, kSiteDvDone, kSiteDkDone, kSiteStDone,
+                kSiteZeroReady, kSiteEpilogue };
+
+template <int DP>
+struct DkdvSmem {
+  static constexpr int kTile = 128 * DP * 2;
+  static constexpr int kDoStages = DP == 128 ? 1 : 2;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTile;
+  static constexpr int kQ = kV + kTile;
+  static constexpr int kDo = kQ + 2 * kTile;
+  static constexpr int kP = kDo + kDoStages * kTile;
+  static constexpr int kDs = kP + 2 * kBlk;
+  static constexpr int kTotal = kDs + 2 * kBlk;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int DP, typename T, int BIAS>
+__global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ DkdvParams p) {
+  using L = DkdvSmem<DP>;
+  using P2 = Pack2<T>;
+  constexpr int KB = DP / 64;
+  constexpr int KS_D = DP / 16;  // K slices of the two "score" products
+  constexpr int kDoStages = L::kDoStages;
+  constexpr uint32_t kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
+  constexpr uint32_t kTmemCols = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t kv_full, q_full[2], q_empty[2], do_full[2], do_empty[2];
+  __shared__ uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done, st_done, zero_ready;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int nb = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H;
+  const int h = bh - b * p.H;
+  const int n0 = nb * 128;
+  const int n_mblk = (p.M + 127) >> 7;
+  const int i_start = p.causal ? min(nb, n_mblk) : 0;
+  const int T_steps = n_mblk - i_start;
+
+  WaitCtx ctx{&abort_flag, p.status, 2};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&do_full[i], 1);
+      mbar_init(&do_empty[i], 1);
+    }
+    mbar_init(&s_full, 1);
+    mbar_init(&dp_full, 1);
+    mbar_init(&p_ready, 8);
+    mbar_init(&ds_ready, 8);
+    mbar_init(&dv_done, 1);
+    mbar_init(&dk_done, 1);
+    mbar_init(&st_done, 1);
+    mbar_init(&zero_ready, 8);
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && live && T_steps > 0) {
+      tma_prefetch_desc(&p.map_q);
+      tma_prefetch_desc(&p.map_k);
+      tma_prefetch_desc(&p.map_v);
+      tma_prefetch_desc(&p.map_do);
+      mbar_expect_tx(&kv_full, 2 * L::kTile);
+      for (int kb = 0; kb < KB; ++kb) {
+        tma_load_4d(smem + L::kK + kb * kBlk, &p.map_k, &kv_full, kb * 64, h, n0, b);
+        tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
+      }
+      bool ok = true;
+      for (int t = 0; t < T_steps && ok; ++t) {
+        const int m0 = (i_start + t) * 128;
+        const int qs = t & 1;
+        if (t >= 2) ok = mbar_wait(&q_empty[qs], ((t >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
+        if (!ok) break;
+        mbar_expect_tx(&q_full[qs], L::kTile);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem + L::kQ + qs * L::kTile + kb * kBlk, &p.map_q, &q_full[qs], kb * 64, h,
+                      m0, b);
+        const int ds = t % kDoStages;
+        const int du = t / kDoStages;
+        if (du >= 1) ok = mbar_wait(&do_empty[ds], (du - 1) & 1, ctx, kSiteDoEmpty, t);
+        if (!ok) break;
+        mbar_expect_tx(&do_full[ds], L::kTile);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem + L::kDo + ds * L::kTile + kb * kBlk, &p.map_do, &do_full[ds], kb * 64,
+                      h, m0, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && live) {
+      constexpr bool bf = P2::kIsBf16;
+      constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
+      constexpr uint32_t idesc_g = make_idesc(bf, true, true, 128, DP);
+      const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
+      const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
+      const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDs);
+      bool ok = true;
+      // zero tiles of dbias above the diagonal (store "phase 0")
+      if (p.write_dbias && p.causal) {
+        ok = mbar_wait(&zero_ready, 0, ctx, kSiteZeroReady, 0);
+        if (ok) {
+          const int nz = min(nb, n_mblk);
+          for (int i = 0; i < nz; ++i) {
+            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
+            if (n0 + 64 < p.N)
+              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
+          }
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+      }
+      mbar_arrive(&st_done);
+      auto issue_s = [&](int t) {
+        const int qs = t & 1;
+        for (int ks = 0; ks < KS_D; ++ks)
+          mma_ss(tmem + kColS, sdesc_kmajor(q_addr + qs * L::kTile, kBlk, ks),
+                 sdesc_kmajor(k_addr, kBlk, ks), idesc_s, ks > 0);
+        mma_commit(&s_full);
+      };
+      auto issue_dp = [&](int t) {
+        const int ds = t % kDoStages;
+        for (int ks = 0; ks < KS_D; ++ks)
+          mma_ss(tmem + kColDp, sdesc_kmajor(do_addr + ds * L::kTile, kBlk, ks),
+                 sdesc_kmajor(v_addr, kBlk, ks), idesc_s, ks > 0);
+        mma_commit(&dp_full);
+      };
+      if (ok && T_steps > 0) {
+        ok = mbar_wait(&kv_full, 0, ctx, kSiteKV, 0);
+        if (ok) ok = mbar_wait(&q_full[0], 0, ctx, kSiteQFull, 0);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+          ok = mbar_wait(&do_full[0], 0, ctx, kSiteDoFull, 0);
+        }
+        if (ok) {
+          tc_fence_after();
+          issue_dp(0);
+        }
+      }
+      for (int t = 0; t < T_steps && ok; ++t) {
+        const int qs = t & 1;
+        const int ds = t % kDoStages;
+        // dV += P^T dO
+        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
+        if (!ok) break;
+        tc_fence_after();
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColDv, sdesc_mnmajor(p_addr, kBlk, ks),
+                 sdesc_mnmajor(do_addr + ds * L::kTile, kBlk, ks), idesc_g, t > 0 || ks > 0);
+        mma_commit(&do_empty[ds]);
+        mma_commit(&dv_done);
+        // S of the next block (its tensor-memory columns are free: P_t was derived from them)
+        if (t + 1 < T_steps) {
+          ok = mbar_wait(&q_full[(t + 1) & 1], ((t + 1) >> 1) & 1, ctx, kSiteQFull, t + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(t + 1);
+        }
+        // the bulk store of dS_{t-1} must have finished reading sDS before dS_t is written
+        if (t >= 1) {
+          if (p.write_dbias) tma_store_wait_read<0>();
+          mbar_arrive(&st_done);
+        }
+        // dK += dS^T Q
+        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
+        if (!ok) break;
+        tc_fence_after();
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColDk, sdesc_mnmajor(ds_addr, kBlk, ks),
+                 sdesc_mnmajor(q_addr + qs * L::kTile, kBlk, ks), idesc_g, t > 0 || ks > 0);
+        mma_commit(&q_empty[qs]);
+        mma_commit(&dk_done);
+        if (p.write_dbias) {
+          const int m0 = (i_start + t) * 128;
+          tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
+          if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
+          tma_store_commit();
+        }
+        // dP of the next block
+        if (t + 1 < T_steps) {
+          const int ds1 = (t + 1) % kDoStages;
+          ok = mbar_wait(&do_full[ds1], ((t + 1) / kDoStages) & 1, ctx, kSiteDoFull, t + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(t + 1);
+        }
+      }
+      tma_store_wait_all<0>();
+    }
+    __syncwarp();
+  } else {
+    // --------------------------------------------------------------- row threads
+    const int r = (warp & 3) * 32 + lane;  // query row inside the block = tensor-memory lane
+    const int hf = warp >> 2;              // column half: keys n0 + 64*hf .. +63
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    bool ok = live;
+    uint8_t* sP = smem + L::kP + hf * kBlk;
+    uint8_t* sDS = smem + L::kDs + hf * kBlk;
+
+    if (p.write_dbias && p.causal && ok) {
+      // zero tile for the causally skipped part of dbias
+      uint4* z = reinterpret_cast<uint4*>(smem + L::kDs);
+      for (int i = tid; i < 2 * kBlk / 16; i += 256) z[i] = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&zero_ready);
+    }
+
+    const int col0 = n0 + hf * 64;
+    const int64_t bias_bh = b * p.bias_sB + h * p.bias_sH;
+    BiasRegs<BIAS> bnext;
+    float lse_next = INFINITY, delta_next = 0.f;
+    auto prefetch = [&](int t) {
+      const int m = (i_start + t) * 128 + r;
+      const bool row_ok = m < p.M;
+      if (BIAS != 0)
+        load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N);
+      lse_next = row_ok ? __ldg(p.lse + (int64_t)bh * p.M + m) : INFINITY;
+      delta_next = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
+    };
+    if (ok && T_steps > 0) prefetch(0);
+
+    for (int t = 0; t < T_steps && ok; ++t) {
+      const int m0 = (i_start + t) * 128;
+      BiasRegs<BIAS> bcur = bnext;
+      const float lse_r = lse_next, delta_r = delta_next;
+      if (t + 1 < T_steps) prefetch(t + 1);
+
+      // ---- P
+      ok = wait_warp(&s_full, t & 1, ctx, kSiteSFull, t);
+      if (!ok) break;
+      tc_fence_after();
+      float pr[64];
+      {
+        uint32_t* su = reinterpret_cast<uint32_t*>(pr);
+        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64), su);
+        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64 + 32), su + 32);
+        tmem_ld_wait();
+      }
+      int limit = p.N - col0;
+      if (p.causal) limit = min(limit, m0 + r - col0 + 1);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float s2;
+        bool keep = i < limit;
+        if (BIAS == 1) {
+          const float2 f = P2::unpack(bcur.w[i >> 1]);
+          s2 = fmaf(pr[i], p.scale_log2, ((i & 1) ? f.y : f.x) * kLog2e);
+        } else if (BIAS == 2) {
+          keep = keep && (((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0);
+          s2 = pr[i] * p.scale_log2;
+        } else {
+          s2 = pr[i] * p.scale_log2;
+        }
+        pr[i] = keep ? ex2(s2 - lse_r) : 0.f;
+      }
+      tc_fence_before();
+      if (t >= 1) {
+        ok = wait_warp(&dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v;
+        v.x = P2::pack(pr[c * 8 + 0], pr[c * 8 + 1]);
+        v.y = P2::pack(pr[c * 8 + 2], pr[c * 8 + 3]);
+        v.z = P2::pack(pr[c * 8 + 4], pr[c * 8 + 5]);
+        v.w = P2::pack(pr[c * 8 + 6], pr[c * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + swz_off(r, c)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+
+      // ---- dS
+      ok = wait_warp(&dp_full, t & 1, ctx, kSiteDpFull, t);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dsu[32];
+      {
+        uint32_t dp[32];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          tmem_ld32(tmem_addr(tmem, lane_base, kColDp + hf * 64 + g * 32), dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float d0 = pr[g * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
+            const float d1 = pr[g * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
+            dsu[g * 16 + i] = P2::pack(d0, d1);
+          }
+        }
+      }
+      tc_fence_before();
+      if (t >= 1) {
+        ok = wait_warp(&dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
+        if (!ok) break;
+      }
+      ok = wait_warp(&st_done, t & 1, ctx, kSiteStDone, t);
+      if (!ok) break;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDS + swz_off(r, c)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_ready);
+    }
+
+    // ---- epilogue: dV, dK (rows = keys) -> global
+    if (ok && T_steps > 0) {
+      ok = wait_warp(&dv_done, (T_steps - 1) & 1, ctx, kSiteEpilogue, 0);
+      if (ok) ok = wait_warp(&dk_done, (T_steps - 1) & 1, ctx, kSiteEpilogue, 1);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int n = n0 + r;
+      constexpr int kHalfCols = DP / 2;  // columns of the head dim this thread stores
+      const int d0 = hf * kHalfCols;
+      T* dkrow = reinterpret_cast<T*>(p.dk) + b * p.dk_sB + (int64_t)n * p.dk_sN + h * p.dk_sH;
+      T* dvrow = reinterpret_cast<T*>(p.dv) + b * p.dv_sB + (int64_t)n * p.dv_sN + h * p.dv_sH;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        T* row = which == 0 ? dvrow : dkrow;
+        const uint32_t colbase = which == 0 ? kColDv : kColDk;
+        const float mul = which == 0 ? 1.0f : p.sm_scale;
+#pragma unroll
+        for (int g = 0; g < kHalfCols / 32; ++g) {
+          uint32_t a[32];
+          if (T_steps > 0) {
+            tmem_ld32(tmem_addr(tmem, lane_base, colbase + d0 + g * 32), a);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = 0;
+          }
+          if (n < p.N) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int d = d0 + g * 32 + c * 8;
+              if (d < p.D) {
+                uint4 v;
+                v.x = P2::pack(__uint_as_float(a[c * 8 + 0]) * mul, __uint_as_float(a[c * 8 + 1]) * mul);
+                v.y = P2::pack(__uint_as_float(a[c * 8 + 2]) * mul, __uint_as_float(a[c * 8 + 3]) * mul);
+                v.z = P2::pack(__uint_as_float(a[c * 8 + 4]) * mul, __uint_as_float(a[c * 8 + 5]) * mul);
+                v.w = P2::pack(__uint_as_float(a[c * 8 + 6]) * mul, __uint_as_float(a[c * 8 + 7]) * mul);
+                *reinterpret_cast<uint4*>(row + d) = v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int DP, typename T, int BIAS>
+int launch_inst(const DkdvParams& kp, dim3 grid, cudaStream_t stream) {
+  using L = DkdvSmem<DP>;
+  auto kern = dkdv_kernel<DP, T, BIAS>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
+        cudaSuccess)
+      return FA_ERR_CUDA;
+    configured[dev] = true;
+  }
+  kern<<<grid, 320, L::kDynamic, stream>>>(kp);
+  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+}
+
+template <int DP, typename T>
+int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t stream) {
+  switch (bias_kind) {
+    case FA_BIAS_NONE: return launch_inst<DP, T, 0>(kp, grid, stream);
+    case FA_BIAS_SAME: return launch_inst<DP, T, 1>(kp, grid, stream);
+    case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(kp, grid, stream);
+    default: return FA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+
+int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
+  DkdvParams kp;
+  int r = make_tmap_bshd(&kp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
+  if (r) return r;
+  r = make_tmap_bshd(&kp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, 128);
+  if (r) return r;
+  r = make_tmap_bshd(&kp.map_v, p.v, p.B, p.N, p.H, p.D, p.v_stride, 128);
+  if (r) return r;
+  r = make_tmap_bshd(&kp.map_do, p.d_o, p.B, p.M, p.H, p.D, p.do_stride, 128);
+  if (r) return r;
+  if (p.write_dbias) {
+    int bm, hm;
+    r = make_tmap_bhmn(&kp.map_dbias, p.dbias, 2, p.B, p.H, p.M, p.N, p.dbias_stride, 64, 128, &bm,
+                       &hm);
+    if (r) return r;
+    if (!bm || !hm) return FA_ERR_ALIGN;  // dbias must be a real (B,H,M,N) tensor
+  } else {
+    kp.map_dbias = kp.map_q;
+  }
+  auto bad = [](const void* ptr, const int64_t s[3]) {
+    return reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || s[0] % 8 || s[1] % 8 || s[2] % 8;
+  };
+  if (bad(p.dk, p.dk_stride) || bad(p.dv, p.dv_stride)) return FA_ERR_ALIGN;
+  if (p.bias_kind != FA_BIAS_NONE) {
+    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
+    if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || (p.bias_stride[0] * eb) % 16 ||
+        (p.bias_stride[1] * eb) % 16 || (p.bias_stride[2] * eb) % 16)
+      return FA_ERR_ALIGN;
+  }
+  kp.bias = p.bias;
+  kp.dk = p.dk;
+  kp.dv = p.dv;
+  kp.lse = p.lse;
+  kp.delta = p.delta;
+  kp.status = status;
+  kp.bias_sB = p.bias_stride[0];
+  kp.bias_sH = p.bias_stride[1];
+  kp.bias_sM = p.bias_stride[2];
+  kp.dk_sB = p.dk_stride[0];
+  kp.dk_sN = p.dk_stride[1];
+  kp.dk_sH = p.dk_stride[2];
+  kp.dv_sB = p.dv_stride[0];
+  kp.dv_sN = p.dv_stride[1];
+  kp.dv_sH = p.dv_stride[2];
+  kp.H = p.H;
+  kp.M = p.M;
+  kp.N = p.N;
+  kp.D = p.D;
+  kp.causal = p.causal ? 1 : 0;
+  kp.write_dbias = p.write_dbias ? 1 : 0;
+  kp.scale_log2 = p.sm_scale * kLog2e;
+  kp.sm_scale = p.sm_scale;
+  const dim3 grid((p.N + 127) / 128, p.B * p.H);
+  const int dp = padded_head_dim(p.D);
+  if (p.dtype == FA_BF16) {
+    return dp == 64 ? launch_bias<64, __nv_bfloat16>(kp, p.bias_kind, grid, stream)
+                    : launch_bias<128, __nv_bfloat16>(kp, p.bias_kind, grid, stream);
+  }
+  return dp == 64 ? launch_bias<64, __half>(kp, p.bias_kind, grid, stream)
+                  : launch_bias<128, __half>(kp, p.bias_kind, grid, stream);
+}
+
+}  // namespace fa

@@ -95,7 +95,7 @@ struct WaitCtx {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
 // Returns true when the phase completed, false when the kernel must bail out.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
                                             int site, int iter) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -402,6 +402,85 @@ struct Pack2<__half> {
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a swizzled tile block.
 __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
   return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
+}
+
+// ----------------------------------------------------------------------------
+// helpers shared by the attention kernels
+// ----------------------------------------------------------------------------
+constexpr int kBlk = 128 * 128;  // bytes of one [128][64] 16-bit tile block (also [128][128] u8)
+
+// All lanes wait, then agree: a warp leaves its loop as a whole.
+__device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+                                          int site, int iter) {
+  const bool ok = mbar_wait(bar, parity, ctx, site, iter);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// 64 bias values of one row half, as raw 16-bit pairs (BIAS == 1) or bytes (BIAS == 2).
+template <int BIAS>
+struct BiasRegs {
+  uint32_t w[BIAS == 1 ? 32 : (BIAS == 2 ? 16 : 1)];
+};
+
+// Reads bias[row][col0 .. col0+63] straight from global memory with 128-bit loads
+// (element-wise at a ragged right edge); out-of-range elements read as zero.
+template <int BIAS>
+__device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bias_base,
+                                              int64_t row_off, bool row_ok, int col0, int N) {
+  if (BIAS == 1) {
+    const uint16_t* rowp = reinterpret_cast<const uint16_t*>(bias_base) + row_off;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int col = col0 + c * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row_ok && col + 8 <= N) {
+        v = __ldg(reinterpret_cast<const uint4*>(rowp + col));
+      } else if (row_ok && col < N) {
+        uint16_t e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = (col + k < N) ? __ldg(rowp + col + k) : (uint16_t)0;
+        v.x = e[0] | ((uint32_t)e[1] << 16);
+        v.y = e[2] | ((uint32_t)e[3] << 16);
+        v.z = e[4] | ((uint32_t)e[5] << 16);
+        v.w = e[6] | ((uint32_t)e[7] << 16);
+      }
+      br.w[c * 4 + 0] = v.x;
+      br.w[c * 4 + 1] = v.y;
+      br.w[c * 4 + 2] = v.z;
+      br.w[c * 4 + 3] = v.w;
+    }
+  } else if (BIAS == 2) {
+    const uint8_t* rowp = reinterpret_cast<const uint8_t*>(bias_base) + row_off;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = col0 + c * 16;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row_ok && col + 16 <= N) {
+        v = __ldg(reinterpret_cast<const uint4*>(rowp + col));
+      } else if (row_ok && col < N) {
+        uint32_t e[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (col + k < N) e[k >> 2] |= (uint32_t)__ldg(rowp + col + k) << (8 * (k & 3));
+        v = make_uint4(e[0], e[1], e[2], e[3]);
+      }
+      br.w[c * 4 + 0] = v.x;
+      br.w[c * 4 + 1] = v.y;
+      br.w[c * 4 + 2] = v.z;
+      br.w[c * 4 + 3] = v.w;
+    }
+  }
+}
+
+// Packs 8 consecutive fp32 values (scaled) into one 16-byte vector of T.
+template <typename P2>
+__device__ __forceinline__ uint4 pack8(const uint32_t* a, float mul) {
+  uint4 v;
+  v.x = P2::pack(__uint_as_float(a[0]) * mul, __uint_as_float(a[1]) * mul);
+  v.y = P2::pack(__uint_as_float(a[2]) * mul, __uint_as_float(a[3]) * mul);
+  v.z = P2::pack(__uint_as_float(a[4]) * mul, __uint_as_float(a[5]) * mul);
+  v.w = P2::pack(__uint_as_float(a[6]) * mul, __uint_as_float(a[7]) * mul);
+  return v;
 }
 
 }  // namespace fa

@@ -1,0 +1,445 @@
+// Forward attention kernel for sm_100a.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
+// 128 keys.  Roles (192 threads):
+//   warps 0-3  softmax: thread t owns query row t (= tensor-memory lane t)
+//   warp 4     TMA producer (one elected lane): Q once, K / V rings, bias ring
+//   warp 5     MMA issuer (one lane) and tensor-memory owner
+// Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
+// in tensor memory, double buffered) -> softmax threads read S_j, add the bias
+// tile (streamed by TMA into a shared-memory ring), apply masks, run the online
+// softmax in the log2 domain and write P_j (16 bit) back into tensor memory over
+// S_j -> O += P_j V_j with P as the tensor-memory operand and V MN-major in
+// shared memory.  S_{j+1} is issued before P_j V_j so the tensor core works
+// while the softmax of block j runs.  The running maximum is only raised when
+// it grows by more than 8 (log2 units); O in tensor memory is rescaled only
+// then.
+//
+// Replaces _attn_fwd / _attn_fwd_inner of the reference (flash_attention.py
+// lines 12-194): same masks (bounds, top-left causal, bool, additive float
+// bias), same base-2 softmax and the same saved log2-domain log-sum-exp.
+#include "fa_common.cuh"
+#include "fa_host.cuh"
+
+namespace fa {
+namespace {
+
+struct FwdParams {
+  CUtensorMap map_q;
+  CUtensorMap map_k;
+  CUtensorMap map_v;
+  CUtensorMap map_bias;
+  void* o;
+  float* lse;
+  int* status;
+  int64_t o_sB, o_sM, o_sH;
+  int H, M, N, D;
+  int causal;
+  int bias_b_mul, bias_h_mul;
+  float scale_log2;  // sm_scale * log2(e)
+};
+
+enum FwdSite { kSiteQ = 1, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty, kSiteSFull,
+               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue };
+
+template <int DP, int BIAS>
+struct FwdSmem {
+  static constexpr int kTile = 128 * DP * 2;
+  static constexpr int kBiasStages = BIAS == 0 ? 0 : 4;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTile;
+  static constexpr int kV = kK + 2 * kTile;
+  static constexpr int kBias = kV + 2 * kTile;
+  static constexpr int kTotal = kBias + kBiasStages * kBlk;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment
+};
+
+template <int DP, typename T, int BIAS>
+__global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+  using L = FwdSmem<DP, BIAS>;
+  using P2 = Pack2<T>;
+  constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
+  constexpr int KS_QK = DP / 16; // MMA K slices of Q K^T
+  constexpr uint32_t kColS = 0, kColO = 256;
+  constexpr uint32_t kTmemCols = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full,
+      pv_done;
+  __shared__ uint64_t bias_full[4], bias_empty[4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int m_block = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H;
+  const int h = bh - b * p.H;
+  const int m0 = m_block * 128;
+
+  int nblk = (p.N + 127) >> 7;
+  if (p.causal) nblk = min(nblk, m_block + 1);
+
+  WaitCtx ctx{&abort_flag, p.status, 1};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(&p_full, 4);
+    mbar_init(&pv_done, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bias_full[i], 1);
+      mbar_init(&bias_empty[i], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  // A kernel launched after an earlier one recorded an error does no work.
+  const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && live) {
+      tma_prefetch_desc(&p.map_q);
+      tma_prefetch_desc(&p.map_k);
+      tma_prefetch_desc(&p.map_v);
+      if (BIAS != 0) tma_prefetch_desc(&p.map_bias);
+      const uint64_t pol_stream = policy_evict_first();
+      mbar_expect_tx(&q_full, L::kTile);
+      for (int kb = 0; kb < KB; ++kb)
+        tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &q_full, kb * 64, h, m0, b);
+      uint32_t unit = 0;
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const int n0 = j * 128;
+        if (j >= 2) ok = mbar_wait(&k_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+        if (!ok) break;
+        mbar_expect_tx(&k_full[st], L::kTile);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
+                      n0, b);
+        if (BIAS != 0) {
+          constexpr int kUnits = BIAS == 1 ? 2 : 1;
+          for (int u = 0; u < kUnits && ok; ++u, ++unit) {
+            const int bs = unit & 3;
+            const uint32_t use = unit >> 2;
+            if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, j);
+            if (!ok) break;
+            mbar_expect_tx(&bias_full[bs], kBlk);
+            tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs],
+                             n0 + u * 64, m0, h * p.bias_h_mul, b * p.bias_b_mul, pol_stream);
+          }
+          if (!ok) break;
+        }
+        if (j >= 2) ok = mbar_wait(&v_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
+        if (!ok) break;
+        mbar_expect_tx(&v_full[st], L::kTile);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
+                      n0, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && live) {
+      constexpr bool bf = P2::kIsBf16;
+      constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 128);
+      constexpr uint32_t idesc_pv = make_idesc(bf, false, true, 128, DP);
+      const uint32_t q_addr = smem_u32(smem + L::kQ);
+      const uint32_t k_addr = smem_u32(smem + L::kK);
+      const uint32_t v_addr = smem_u32(smem + L::kV);
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        for (int ks = 0; ks < KS_QK; ++ks)
+          mma_ss(tmem + kColS + st * 128, sdesc_kmajor(q_addr, kBlk, ks),
+                 sdesc_kmajor(k_addr + st * L::kTile, kBlk, ks), idesc_qk, ks > 0);
+        mma_commit(&s_full[st]);
+        mma_commit(&k_empty[st]);
+      };
+      bool ok = mbar_wait(&q_full, 0, ctx, kSiteQ, 0);
+      if (ok) ok = mbar_wait(&k_full[0], 0, ctx, kSiteKFull, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < nblk) {
+          ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, kSiteKFull, j + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
+        ok = mbar_wait(&v_full[st], (j >> 1) & 1, ctx, kSiteVFull, j);
+        if (!ok) break;
+        ok = mbar_wait(&p_full, j & 1, ctx, kSitePFull, j);
+        if (!ok) break;
+        tc_fence_after();
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + kColO, tmem + kColS + st * 128 + ks * 8,
+                 sdesc_mnmajor(v_addr + st * L::kTile, kBlk, ks), idesc_pv, j > 0 || ks > 0);
+        mma_commit(&v_empty[st]);
+        mma_commit(&pv_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------- softmax
+    const int r = tid;  // row of the tile, tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = live;
+    uint32_t unit = 0;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int st = j & 1;
+      const int n0 = j * 128;
+      ok = wait_warp(&s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
+      if (!ok) break;
+      tc_fence_after();
+      float s[128];
+      {
+        uint32_t* su = reinterpret_cast<uint32_t*>(s);
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + g * 32), su + g * 32);
+        tmem_ld_wait();
+      }
+      // ---- scale, bias / mask
+      if (BIAS == 0) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] *= p.scale_log2;
+      } else if (BIAS == 1) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u, ++unit) {
+          const int bs = unit & 3;
+          ok = wait_warp(&bias_full[bs], (unit >> 2) & 1, ctx, kSiteBiasFull, j);
+          if (!ok) break;
+          const uint8_t* tile = smem + L::kBias + bs * kBlk;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, c));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = P2::unpack(w[e]);
+              const int i = u * 64 + c * 8 + e * 2;
+              s[i] = fmaf(s[i], p.scale_log2, f.x * kLog2e);
+              s[i + 1] = fmaf(s[i + 1], p.scale_log2, f.y * kLog2e);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bias_empty[bs]);
+        }
+        if (!ok) break;
+      } else {
+        const int bs = unit & 3;
+        ok = wait_warp(&bias_full[bs], (unit >> 2) & 1, ctx, kSiteBiasFull, j);
+        if (!ok) break;
+        const uint8_t* tile = smem + L::kBias + bs * kBlk;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, c));
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int i = c * 16 + e * 4 + k;
+              const bool keep = ((w[e] >> (8 * k)) & 0xFFu) != 0;
+              s[i] = keep ? s[i] * p.scale_log2 : -INFINITY;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bias_empty[bs]);
+        ++unit;
+      }
+      // ---- bounds and causal masks (only on blocks that need them)
+      {
+        int limit = p.N - n0;
+        if (p.causal) limit = min(limit, m0 + r - n0 + 1);
+        const bool block_needs = (n0 + 128 > p.N) || (p.causal && n0 + 127 > m0);
+        if (block_needs) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (i >= limit) s[i] = -INFINITY;
+        }
+      }
+      // ---- online softmax
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      const bool need = mx > m_used + 8.0f;
+      const bool any_need = __any_sync(0xffffffffu, need);
+      // P_{j} overwrites S_j; O may only be touched once P_{j-1} V_{j-1} has completed.
+      if (j > 0) {
+        ok = wait_warp(&pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
+        if (!ok) break;
+      }
+      if (any_need) {
+        const float m_new = need ? mx : m_used;
+        const float alpha = need ? ex2(m_used - m_new) : 1.0f;
+        l *= alpha;
+        m_used = m_new;
+        if (j > 0) {
+          tc_fence_after();
+#pragma unroll
+          for (int g = 0; g < DP / 32; ++g) {
+            uint32_t o[32];
+            tmem_ld32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+          }
+        }
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float p0 = ex2(s[2 * i] - m_eff);
+        const float p1 = ex2(s[2 * i + 1] - m_eff);
+        sum += p0 + p1;
+        pk[i] = P2::pack(p0, p1);
+      }
+      l += sum;
+      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128), pk);
+      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128 + 32), pk + 32);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+    }
+    // ---- epilogue: O / l -> global, log-sum-exp
+    if (ok) ok = wait_warp(&pv_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
+    if (ok) {
+      tc_fence_after();
+      const int m = m0 + r;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM +
+                h * p.o_sH;
+#pragma unroll
+      for (int g = 0; g < DP / 32; ++g) {
+        uint32_t o[32];
+        tmem_ld32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+        tmem_ld_wait();
+        if (m < p.M) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (g * 32 + c * 8 < p.D) {
+              uint4 v;
+              v.x = P2::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+              v.y = P2::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+              v.z = P2::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+              v.w = P2::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + g * 32 + c * 8) = v;
+            }
+          }
+        }
+      }
+      if (m < p.M)
+        p.lse[(static_cast<int64_t>(bh)) * p.M + m] = l > 0.f ? m_used + log2f(l) : INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int DP, typename T, int BIAS>
+int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
+  using L = FwdSmem<DP, BIAS>;
+  auto kern = fwd_kernel<DP, T, BIAS>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
+        cudaSuccess)
+      return FA_ERR_CUDA;
+    configured[dev] = true;
+  }
+  kern<<<grid, 192, L::kDynamic, stream>>>(fp);
+  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+}
+
+template <int DP, typename T>
+int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stream) {
+  switch (bias_kind) {
+    case FA_BIAS_NONE: return launch_inst<DP, T, 0>(fp, grid, stream);
+    case FA_BIAS_SAME: return launch_inst<DP, T, 1>(fp, grid, stream);
+    case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(fp, grid, stream);
+    default: return FA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+
+int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
+  FwdParams fp;
+  int r = make_tmap_bshd(&fp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
+  if (r) return r;
+  r = make_tmap_bshd(&fp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, 128);
+  if (r) return r;
+  r = make_tmap_bshd(&fp.map_v, p.v, p.B, p.N, p.H, p.D, p.v_stride, 128);
+  if (r) return r;
+  fp.bias_b_mul = fp.bias_h_mul = 0;
+  if (p.bias_kind == FA_BIAS_SAME) {
+    r = make_tmap_bhmn(&fp.map_bias, p.bias, 2, p.B, p.H, p.M, p.N, p.bias_stride, 64, 128,
+                       &fp.bias_b_mul, &fp.bias_h_mul);
+    if (r) return r;
+  } else if (p.bias_kind == FA_BIAS_BOOL) {
+    r = make_tmap_bhmn(&fp.map_bias, p.bias, 1, p.B, p.H, p.M, p.N, p.bias_stride, 128, 128,
+                       &fp.bias_b_mul, &fp.bias_h_mul);
+    if (r) return r;
+  } else {
+    fp.map_bias = fp.map_q;
+  }
+  if (reinterpret_cast<uintptr_t>(p.o) % 16 != 0 || p.o_stride[0] % 8 || p.o_stride[1] % 8 ||
+      p.o_stride[2] % 8)
+    return FA_ERR_ALIGN;
+  fp.o = p.o;
+  fp.lse = p.lse;
+  fp.status = status;
+  fp.o_sB = p.o_stride[0];
+  fp.o_sM = p.o_stride[1];
+  fp.o_sH = p.o_stride[2];
+  fp.H = p.H;
+  fp.M = p.M;
+  fp.N = p.N;
+  fp.D = p.D;
+  fp.causal = p.causal ? 1 : 0;
+  fp.scale_log2 = p.sm_scale * kLog2e;
+  const dim3 grid((p.M + 127) / 128, p.B * p.H);
+  const int dp = padded_head_dim(p.D);
+  if (p.dtype == FA_BF16) {
+    return dp == 64 ? launch_bias<64, __nv_bfloat16>(fp, p.bias_kind, grid, stream)
+                    : launch_bias<128, __nv_bfloat16>(fp, p.bias_kind, grid, stream);
+  }
+  return dp == 64 ? launch_bias<64, __half>(fp, p.bias_kind, grid, stream)
+                  : launch_bias<128, __half>(fp, p.bias_kind, grid, stream);
+}
+
+}  // namespace fa
