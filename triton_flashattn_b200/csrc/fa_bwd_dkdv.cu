@@ -42,14 +42,14 @@ struct DkdvParams {
   int64_t bias_sB, bias_sH, bias_sM;
   int64_t dk_sB, dk_sN, dk_sH, dv_sB, dv_sN, dv_sH;
   int H, M, N, D;
-  int causal, write_dbias;
+  int causal, write_dbias, bias_vec32;
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
 };
 
 enum DkdvSite { kSiteKV = 1, kSiteQFull, kSiteQEmpty, kSiteDoFull, kSiteDoEmpty, kSiteSFull,
                 kSiteDpFull, kSitePReady, kSiteDsReady, kSiteDvDone, kSiteDkDone, kSiteStDone,
-                kSiteZeroReady, kSiteEpilogue };
+                kSiteZeroReady, kSiteEpilogue, kSiteSFree, kSiteDpFree };
 
 template <int DP>
 struct DkdvSmem {
@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t kv_full, q_full[2], q_empty[2], do_full[2], do_empty[2];
   __shared__ uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done, st_done, zero_ready;
+  __shared__ uint64_t s_free, dp_free;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -114,6 +115,8 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     mbar_init(&dk_done, 1);
     mbar_init(&st_done, 1);
     mbar_init(&zero_ready, 8);
+    mbar_init(&s_free, 8);
+    mbar_init(&dp_free, 8);
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -183,18 +186,20 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         }
       }
       mbar_arrive(&st_done);
+      // slice-0 descriptors: K-major views (S, dP) and MN-major views (dV, dK)
+      const uint64_t k_km = make_sdesc(k_addr, 0, 1024), v_km = make_sdesc(v_addr, 0, 1024);
+      const uint64_t q_km_0 = make_sdesc(q_addr, 0, 1024), q_km_1 = make_sdesc(q_addr + L::kTile, 0, 1024);
+      const uint64_t q_mn_0 = make_sdesc(q_addr, kBlk, 1024), q_mn_1 = make_sdesc(q_addr + L::kTile, kBlk, 1024);
+      const uint64_t do_km_0 = make_sdesc(do_addr, 0, 1024), do_km_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, 0, 1024);
+      const uint64_t do_mn_0 = make_sdesc(do_addr, kBlk, 1024), do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
+      const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
       auto issue_s = [&](int t) {
-        const int qs = t & 1;
-        for (int ks = 0; ks < KS_D; ++ks)
-          mma_ss(tmem + kColS, sdesc_kmajor(q_addr + qs * L::kTile, kBlk, ks),
-                 sdesc_kmajor(k_addr, kBlk, ks), idesc_s, ks > 0);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColS, ((t & 1) ? q_km_1 : q_km_0), k_km, kBlk, kBlk, idesc_s, false);
         mma_commit(&s_full);
       };
       auto issue_dp = [&](int t) {
-        const int ds = t % kDoStages;
-        for (int ks = 0; ks < KS_D; ++ks)
-          mma_ss(tmem + kColDp, sdesc_kmajor(do_addr + ds * L::kTile, kBlk, ks),
-                 sdesc_kmajor(v_addr, kBlk, ks), idesc_s, ks > 0);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ((t % kDoStages) ? do_km_1 : do_km_0), v_km, kBlk, kBlk,
+                                          idesc_s, false);
         mma_commit(&dp_full);
       };
       if (ok && T_steps > 0) {
@@ -213,22 +218,21 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
       for (int t = 0; t < T_steps && ok; ++t) {
         const int qs = t & 1;
         const int ds = t % kDoStages;
-        // dV += P^T dO
-        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
-        if (!ok) break;
-        tc_fence_after();
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColDv, sdesc_mnmajor(p_addr, kBlk, ks),
-                 sdesc_mnmajor(do_addr + ds * L::kTile, kBlk, ks), idesc_g, t > 0 || ks > 0);
-        mma_commit(&do_empty[ds]);
-        mma_commit(&dv_done);
-        // S of the next block (its tensor-memory columns are free: P_t was derived from them)
+        // S of the next block as soon as the row threads hold S_t in registers
         if (t + 1 < T_steps) {
-          ok = mbar_wait(&q_full[(t + 1) & 1], ((t + 1) >> 1) & 1, ctx, kSiteQFull, t + 1);
+          ok = mbar_wait(&s_free, t & 1, ctx, kSiteSFree, t);
+          if (ok) ok = mbar_wait(&q_full[(t + 1) & 1], ((t + 1) >> 1) & 1, ctx, kSiteQFull, t + 1);
           if (!ok) break;
           tc_fence_after();
           issue_s(t + 1);
         }
+        // dV += P^T dO
+        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
+        if (!ok) break;
+        tc_fence_after();
+        issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ((ds) ? do_mn_1 : do_mn_0), kBlk, kBlk, idesc_g, t > 0);
+        mma_commit(&do_empty[ds]);
+        mma_commit(&dv_done);
         // the bulk store of dS_{t-1} must have finished reading sDS before dS_t is written
         if (t >= 1) {
           if (p.write_dbias) tma_store_wait_read<0>();
@@ -238,9 +242,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
         if (!ok) break;
         tc_fence_after();
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColDk, sdesc_mnmajor(ds_addr, kBlk, ks),
-                 sdesc_mnmajor(q_addr + qs * L::kTile, kBlk, ks), idesc_g, t > 0 || ks > 0);
+        issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, ((qs) ? q_mn_1 : q_mn_0), kBlk, kBlk, idesc_g, t > 0);
         mma_commit(&q_empty[qs]);
         mma_commit(&dk_done);
         if (p.write_dbias) {
@@ -249,10 +251,11 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
           if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
           tma_store_commit();
         }
-        // dP of the next block
+        // dP of the next block (its columns were handed back before dS_t was written)
         if (t + 1 < T_steps) {
           const int ds1 = (t + 1) % kDoStages;
-          ok = mbar_wait(&do_full[ds1], ((t + 1) / kDoStages) & 1, ctx, kSiteDoFull, t + 1);
+          ok = mbar_wait(&dp_free, t & 1, ctx, kSiteDpFree, t);
+          if (ok) ok = mbar_wait(&do_full[ds1], ((t + 1) / kDoStages) & 1, ctx, kSiteDoFull, t + 1);
           if (!ok) break;
           tc_fence_after();
           issue_dp(t + 1);
@@ -282,13 +285,14 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     const int col0 = n0 + hf * 64;
     const int64_t bias_bh = b * p.bias_sB + h * p.bias_sH;
     BiasRegs<BIAS> bnext;
-    float lse_next = INFINITY, delta_next = 0.f;
+    float lse_next = -INFINITY, delta_next = 0.f;  // lse_next holds -LSE2 of the row
     auto prefetch = [&](int t) {
       const int m = (i_start + t) * 128 + r;
       const bool row_ok = m < p.M;
       if (BIAS != 0)
-        load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N);
-      lse_next = row_ok ? __ldg(p.lse + (int64_t)bh * p.M + m) : INFINITY;
+        load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N,
+                             p.bias_vec32 != 0);
+      lse_next = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
       delta_next = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
     };
     if (ok && T_steps > 0) prefetch(0);
@@ -296,7 +300,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     for (int t = 0; t < T_steps && ok; ++t) {
       const int m0 = (i_start + t) * 128;
       BiasRegs<BIAS> bcur = bnext;
-      const float lse_r = lse_next, delta_r = delta_next;
+      const float neg_lse = lse_next, delta_r = delta_next;
       if (t + 1 < T_steps) prefetch(t + 1);
 
       // ---- P
@@ -310,24 +314,30 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64 + 32), su + 32);
         tmem_ld_wait();
       }
-      int limit = p.N - col0;
-      if (p.causal) limit = min(limit, m0 + r - col0 + 1);
+      // S_t now lives in registers: hand its columns back for S_{t+1}
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free);
+      // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have -LSE2 = -inf
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        float s2;
-        bool keep = i < limit;
         if (BIAS == 1) {
           const float2 f = P2::unpack(bcur.w[i >> 1]);
-          s2 = fmaf(pr[i], p.scale_log2, ((i & 1) ? f.y : f.x) * kLog2e);
+          pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
         } else if (BIAS == 2) {
-          keep = keep && (((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0);
-          s2 = pr[i] * p.scale_log2;
+          const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
+          pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
         } else {
-          s2 = pr[i] * p.scale_log2;
+          pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
         }
-        pr[i] = keep ? ex2(s2 - lse_r) : 0.f;
       }
-      tc_fence_before();
+      if ((col0 + 64 > p.N) || (p.causal && col0 + 63 > m0)) {
+        int limit = p.N - col0;
+        if (p.causal) limit = min(limit, m0 + r - col0 + 1);
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= limit) pr[i] = 0.f;
+      }
       if (t >= 1) {
         ok = wait_warp(&dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
         if (!ok) break;
@@ -365,6 +375,8 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         }
       }
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dp_free);
       if (t >= 1) {
         ok = wait_warp(&dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
         if (!ok) break;
@@ -511,6 +523,12 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   kp.D = p.D;
   kp.causal = p.causal ? 1 : 0;
   kp.write_dbias = p.write_dbias ? 1 : 0;
+  {
+    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
+    kp.bias_vec32 = p.bias_kind != FA_BIAS_NONE && reinterpret_cast<uintptr_t>(p.bias) % 32 == 0 &&
+                    (p.bias_stride[0] * eb) % 32 == 0 && (p.bias_stride[1] * eb) % 32 == 0 &&
+                    (p.bias_stride[2] * eb) % 32 == 0;
+  }
   kp.scale_log2 = p.sm_scale * kLog2e;
   kp.sm_scale = p.sm_scale;
   const dim3 grid((p.N + 127) / 128, p.B * p.H);

@@ -39,7 +39,7 @@ struct DqParams {
   int64_t bias_sB, bias_sH, bias_sM;
   int64_t dq_sB, dq_sM, dq_sH;
   int H, M, N, D;
-  int causal;
+  int causal, bias_vec32;
   float scale_log2;
   float sm_scale;
 };
@@ -156,20 +156,20 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
       const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
       const uint32_t ds_addr = smem_u32(smem + L::kDs);
+      const uint64_t q_km = make_sdesc(q_addr, 0, 1024), do_km = make_sdesc(do_addr, 0, 1024);
+      const uint64_t k_km_0 = make_sdesc(k_addr, 0, 1024), k_km_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
+      const uint64_t k_mn_0 = make_sdesc(k_addr, kBlk, 1024), k_mn_1 = make_sdesc(k_addr + L::kTile, kBlk, 1024);
+      const uint64_t v_km_0 = make_sdesc(v_addr, 0, 1024), v_km_1 = make_sdesc(v_addr + L::kTile, 0, 1024);
+      const uint64_t ds_km = make_sdesc(ds_addr, 0, 1024);
       auto issue_s = [&](int j) {
-        const int st = j & 1;
-        for (int ks = 0; ks < KS_D; ++ks)
-          mma_ss(tmem + kColS, sdesc_kmajor(q_addr, kBlk, ks),
-                 sdesc_kmajor(k_addr + st * L::kTile, kBlk, ks), idesc_s, ks > 0);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, ((j & 1) ? k_km_1 : k_km_0), kBlk, kBlk, idesc_s, false);
         mma_commit(&s_full);
       };
       auto issue_dp = [&](int j) {
-        const int st = j & 1;
-        for (int ks = 0; ks < KS_D; ++ks)
-          mma_ss(tmem + kColDp, sdesc_kmajor(do_addr, kBlk, ks),
-                 sdesc_kmajor(v_addr + st * L::kTile, kBlk, ks), idesc_s, ks > 0);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, ((j & 1) ? v_km_1 : v_km_0), kBlk, kBlk, idesc_s,
+                                          false);
         mma_commit(&dp_full);
-        mma_commit(&v_empty[st]);
+        mma_commit(&v_empty[j & 1]);
       };
       bool ok = mbar_wait(&qdo_full, 0, ctx, kSiteQdo, 0);
       if (ok) ok = mbar_wait(&k_full[0], 0, ctx, kSiteKFull, 0);
@@ -201,9 +201,7 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
         ok = mbar_wait(&ds_ready, j & 1, ctx, kSiteDsReady, j);
         if (!ok) break;
         tc_fence_after();
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColDq, sdesc_kmajor(ds_addr, kBlk, ks),
-                 sdesc_mnmajor(k_addr + st * L::kTile, kBlk, ks), idesc_dq, j > 0 || ks > 0);
+        issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, ((st) ? k_mn_1 : k_mn_0), kBlk, kBlk, idesc_dq, j > 0);
         mma_commit(&k_empty[st]);
         mma_commit(&dq_done);
       }
@@ -219,16 +217,16 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
     bool ok = live;
     uint8_t* sDS = smem + L::kDs + hf * kBlk;
     const int64_t bias_row = b * p.bias_sB + h * p.bias_sH + (int64_t)m * p.bias_sM;
-    const float lse_r = row_ok ? __ldg(p.lse + (int64_t)bh * p.M + m) : INFINITY;
+    const float neg_lse = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
     const float delta_r = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
     BiasRegs<BIAS> bnext;
-    if (ok && BIAS != 0) load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, hf * 64, p.N);
+    if (ok && BIAS != 0) load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, hf * 64, p.N, p.bias_vec32 != 0);
 
     for (int j = 0; j < nblk && ok; ++j) {
       const int col0 = j * 128 + hf * 64;
       BiasRegs<BIAS> bcur = bnext;
       if (BIAS != 0 && j + 1 < nblk)
-        load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, col0 + 128, p.N);
+        load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, col0 + 128, p.N, p.bias_vec32 != 0);
 
       ok = wait_warp(&s_full, j & 1, ctx, kSiteSFull, j);
       if (!ok) break;
@@ -244,22 +242,24 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free);
 
-      int limit = p.N - col0;
-      if (p.causal) limit = min(limit, m - col0 + 1);
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        float s2;
-        bool keep = i < limit;
         if (BIAS == 1) {
           const float2 f = P2::unpack(bcur.w[i >> 1]);
-          s2 = fmaf(pr[i], p.scale_log2, ((i & 1) ? f.y : f.x) * kLog2e);
+          pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
         } else if (BIAS == 2) {
-          keep = keep && (((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0);
-          s2 = pr[i] * p.scale_log2;
+          const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
+          pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
         } else {
-          s2 = pr[i] * p.scale_log2;
+          pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
         }
-        pr[i] = keep ? ex2(s2 - lse_r) : 0.f;
+      }
+      if ((col0 + 64 > p.N) || (p.causal && col0 + 63 > m0)) {
+        int limit = p.N - col0;
+        if (p.causal) limit = min(limit, m - col0 + 1);
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= limit) pr[i] = 0.f;
       }
 
       ok = wait_warp(&dp_full, j & 1, ctx, kSiteDpFull, j);
@@ -414,9 +414,8 @@ __global__ void __launch_bounds__(192, 2) dq_from_ds_kernel(const __grid_constan
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + st * L::kStage);
         const uint32_t b_addr = a_addr + L::kDsBytes;
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem, sdesc_kmajor(a_addr, 0, ks), sdesc_mnmajor(b_addr, 64 * 128, ks), idesc,
-                 s > 0 || ks > 0);
+        issue_gemm_ss<4, false, true>(tmem, make_sdesc(a_addr, 0, 1024),
+                                      make_sdesc(b_addr, 64 * 128, 1024), 0, 0, idesc, s > 0);
         mma_commit(&empty[st]);
       }
       if (ok) mma_commit(&acc_done);
@@ -549,6 +548,12 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   kp.N = p.N;
   kp.D = p.D;
   kp.causal = p.causal ? 1 : 0;
+  {
+    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
+    kp.bias_vec32 = p.bias_kind != FA_BIAS_NONE && reinterpret_cast<uintptr_t>(p.bias) % 32 == 0 &&
+                    (p.bias_stride[0] * eb) % 32 == 0 && (p.bias_stride[1] * eb) % 32 == 0 &&
+                    (p.bias_stride[2] * eb) % 32 == 0;
+  }
   kp.scale_log2 = p.sm_scale * kLog2e;
   kp.sm_scale = p.sm_scale;
   const dim3 grid((p.M + 127) / 128, p.B * p.H);

@@ -327,6 +327,15 @@ __device__ __forceinline__ uint64_t sdesc_mnmajor(uint32_t tile_addr, uint32_t b
   return make_sdesc(a, block_bytes, 1024);
 }
 
+// Offsets (in descriptor units of 16 bytes) of K slice `ks` relative to slice 0;
+// adding them to a base descriptor only touches the start-address field.
+__host__ __device__ constexpr uint64_t kmajor_step(int ks, uint32_t block_bytes) {
+  return (static_cast<uint64_t>(ks >> 2) * block_bytes + static_cast<uint64_t>(ks & 3) * 32u) >> 4;
+}
+__host__ __device__ constexpr uint64_t mnmajor_step(int ks) {
+  return (static_cast<uint64_t>(ks) * 2048u) >> 4;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                        uint32_t idesc, bool accumulate) {
@@ -357,6 +366,32 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
                : "memory");
+}
+
+// One tile product as KS unrolled tcgen05.mma instructions (K = 16 each).  The
+// descriptors of slice 0 are computed once by the caller; per slice only a
+// constant is added, so the issuing thread spends a few instructions per MMA.
+template <int KS, bool A_MN, bool B_MN>
+__device__ __forceinline__ void issue_gemm_ss(uint32_t d_tmem, uint64_t a_base, uint64_t b_base,
+                                              uint32_t a_block_bytes, uint32_t b_block_bytes,
+                                              uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const uint64_t a = a_base + (A_MN ? mnmajor_step(ks) : kmajor_step(ks, a_block_bytes));
+    const uint64_t b = b_base + (B_MN ? mnmajor_step(ks) : kmajor_step(ks, b_block_bytes));
+    mma_ss(d_tmem, a, b, idesc, accumulate || ks > 0);
+  }
+}
+// Same with the A operand in tensor memory (16-bit pairs, 8 columns per K slice).
+template <int KS, bool B_MN>
+__device__ __forceinline__ void issue_gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_base,
+                                              uint32_t b_block_bytes, uint32_t idesc,
+                                              bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const uint64_t b = b_base + (B_MN ? mnmajor_step(ks) : kmajor_step(ks, b_block_bytes));
+    mma_ts(d_tmem, a_tmem + ks * 8, b, idesc, accumulate || ks > 0);
+  }
 }
 
 // ----------------------------------------------------------------------------
@@ -404,6 +439,25 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
   return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads'.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// 32-byte (one full sector) read-only global load that bypasses L1.
+__device__ __forceinline__ void ldg256(const void* ptr, uint32_t* r) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "l"(ptr));
+}
+
 // ----------------------------------------------------------------------------
 // helpers shared by the attention kernels
 // ----------------------------------------------------------------------------
@@ -422,53 +476,53 @@ struct BiasRegs {
   uint32_t w[BIAS == 1 ? 32 : (BIAS == 2 ? 16 : 1)];
 };
 
-// Reads bias[row][col0 .. col0+63] straight from global memory with 128-bit loads
-// (element-wise at a ragged right edge); out-of-range elements read as zero.
+// Reads bias[row][col0 .. col0+63] straight from global memory; out-of-range elements
+// read as zero.  `vec32` (uniform): rows are 32-byte aligned, so whole sectors are
+// fetched with 256-bit loads; otherwise 128-bit loads; element-wise at a ragged edge.
 template <int BIAS>
 __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bias_base,
-                                              int64_t row_off, bool row_ok, int col0, int N) {
-  if (BIAS == 1) {
-    const uint16_t* rowp = reinterpret_cast<const uint16_t*>(bias_base) + row_off;
+                                              int64_t row_off, bool row_ok, int col0, int N,
+                                              bool vec32) {
+  constexpr int kElem = BIAS == 1 ? 2 : 1;        // bytes per element
+  constexpr int kWords = BIAS == 1 ? 32 : 16;     // 32-bit words per 64 elements
+  constexpr int kPerWord = 4 / kElem;             // elements per word
+  if (BIAS == 0) return;
+  const uint8_t* rowp = reinterpret_cast<const uint8_t*>(bias_base) + row_off * kElem;
+  if (!row_ok || col0 >= N) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int col = col0 + c * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row_ok && col + 8 <= N) {
-        v = __ldg(reinterpret_cast<const uint4*>(rowp + col));
-      } else if (row_ok && col < N) {
-        uint16_t e[8];
+    for (int i = 0; i < kWords; ++i) br.w[i] = 0;
+    return;
+  }
+  if (col0 + 64 <= N) {
+    if (vec32) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) e[k] = (col + k < N) ? __ldg(rowp + col + k) : (uint16_t)0;
-        v.x = e[0] | ((uint32_t)e[1] << 16);
-        v.y = e[2] | ((uint32_t)e[3] << 16);
-        v.z = e[4] | ((uint32_t)e[5] << 16);
-        v.w = e[6] | ((uint32_t)e[7] << 16);
+      for (int c = 0; c < kWords / 8; ++c) ldg256(rowp + (col0 * kElem) + c * 32, br.w + c * 8);
+    } else {
+#pragma unroll
+      for (int c = 0; c < kWords / 4; ++c) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(rowp + (col0 * kElem) + c * 16));
+        br.w[c * 4 + 0] = v.x;
+        br.w[c * 4 + 1] = v.y;
+        br.w[c * 4 + 2] = v.z;
+        br.w[c * 4 + 3] = v.w;
       }
-      br.w[c * 4 + 0] = v.x;
-      br.w[c * 4 + 1] = v.y;
-      br.w[c * 4 + 2] = v.z;
-      br.w[c * 4 + 3] = v.w;
     }
-  } else if (BIAS == 2) {
-    const uint8_t* rowp = reinterpret_cast<const uint8_t*>(bias_base) + row_off;
+    return;
+  }
+  // ragged right edge: element-wise
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int col = col0 + c * 16;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row_ok && col + 16 <= N) {
-        v = __ldg(reinterpret_cast<const uint4*>(rowp + col));
-      } else if (row_ok && col < N) {
-        uint32_t e[4] = {0, 0, 0, 0};
+  for (int i = 0; i < kWords; ++i) {
+    uint32_t word = 0;
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (col + k < N) e[k >> 2] |= (uint32_t)__ldg(rowp + col + k) << (8 * (k & 3));
-        v = make_uint4(e[0], e[1], e[2], e[3]);
+    for (int k = 0; k < kPerWord; ++k) {
+      const int col = col0 + i * kPerWord + k;
+      if (col < N) {
+        const uint32_t e = BIAS == 1 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rowp) + col)
+                                     : (uint32_t)__ldg(rowp + col);
+        word |= e << (8 * kElem * k);
       }
-      br.w[c * 4 + 0] = v.x;
-      br.w[c * 4 + 1] = v.y;
-      br.w[c * 4 + 2] = v.z;
-      br.w[c * 4 + 3] = v.w;
     }
+    br.w[i] = word;
   }
 }
 

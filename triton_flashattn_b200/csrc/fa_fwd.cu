@@ -1,10 +1,12 @@
 // Forward attention kernel for sm_100a.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
-// 128 keys.  Roles (192 threads):
-//   warps 0-3  softmax: thread t owns query row t (= tensor-memory lane t)
-//   warp 4     TMA producer (one elected lane): Q once, K / V rings, bias ring
-//   warp 5     MMA issuer (one lane) and tensor-memory owner
+// 128 keys.  Roles (320 threads):
+//   warps 0-7  softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
+//              lanes) and the 64-key half (w>>2) of every block; the two halves of
+//              a row exchange their partial maxima through shared memory
+//   warp 8     TMA producer (one elected lane): Q once, K / V rings, bias ring
+//   warp 9     MMA issuer (one lane) and tensor-memory owner
 // Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
 // in tensor memory, double buffered) -> softmax threads read S_j, add the bias
 // tile (streamed by TMA into a shared-memory ring), apply masks, run the online
@@ -36,16 +38,17 @@ struct FwdParams {
   int H, M, N, D;
   int causal;
   int bias_b_mul, bias_h_mul;
-  float scale_log2;  // sm_scale * log2(e)
+  float sm_scale;
 };
 
 enum FwdSite { kSiteQ = 1, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty, kSiteSFull,
-               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue };
+               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue, kSitePair };
 
 template <int DP, int BIAS>
 struct FwdSmem {
   static constexpr int kTile = 128 * DP * 2;
-  static constexpr int kBiasStages = BIAS == 0 ? 0 : 4;
+  // 16 KB bias units (one 64-key column half each); 3 at D=128 to stay inside 227 KB
+  static constexpr int kBiasStages = BIAS == 0 ? 0 : (DP == 128 ? 3 : 4);
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + kTile;
   static constexpr int kV = kK + 2 * kTile;
@@ -55,11 +58,13 @@ struct FwdSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
   constexpr int KS_QK = DP / 16; // MMA K slices of Q K^T
+  constexpr int kHalfD = DP / 2; // output columns handled by one softmax thread
+  constexpr uint32_t NB = L::kBiasStages > 0 ? L::kBiasStages : 1;
   constexpr uint32_t kColS = 0, kColO = 256;
   constexpr uint32_t kTmemCols = 512;
 
@@ -68,7 +73,8 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full,
       pv_done;
-  __shared__ uint64_t bias_full[4], bias_empty[4];
+  __shared__ uint64_t bias_full[4], bias_empty[4], pair_bars[4];
+  __shared__ float xchg[2][2][128];  // [step parity][column half][row]: partial row maxima / sums
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -96,15 +102,16 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    mbar_init(&p_full, 4);
+    mbar_init(&p_full, 8);
     mbar_init(&pv_done, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bias_full[i], 1);
-      mbar_init(&bias_empty[i], 4);
+      mbar_init(&bias_empty[i], BIAS == 2 ? 8 : 4);
+      mbar_init(&pair_bars[i], 2);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
   // A kernel launched after an earlier one recorded an error does no work.
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && live) {
       tma_prefetch_desc(&p.map_q);
@@ -138,10 +145,12 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
           tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
                       n0, b);
         if (BIAS != 0) {
+          // 16 KB units: 16-bit bias -> one per 64-key column half ([128 rows][64 keys]);
+          // byte mask -> one per block ([128 rows][128 keys]) shared by both halves
           constexpr int kUnits = BIAS == 1 ? 2 : 1;
           for (int u = 0; u < kUnits && ok; ++u, ++unit) {
-            const int bs = unit & 3;
-            const uint32_t use = unit >> 2;
+            const int bs = unit % NB;
+            const uint32_t use = unit / NB;
             if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, j);
             if (!ok) break;
             mbar_expect_tx(&bias_full[bs], kBlk);
@@ -158,7 +167,7 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
                       n0, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
@@ -167,11 +176,13 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
       const uint32_t q_addr = smem_u32(smem + L::kQ);
       const uint32_t k_addr = smem_u32(smem + L::kK);
       const uint32_t v_addr = smem_u32(smem + L::kV);
+      const uint64_t q_desc = make_sdesc(q_addr, 0, 1024);
+      const uint64_t k_desc_0 = make_sdesc(k_addr, 0, 1024), k_desc_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
+      const uint64_t v_desc_0 = make_sdesc(v_addr, kBlk, 1024), v_desc_1 = make_sdesc(v_addr + L::kTile, kBlk, 1024);
       auto issue_qk = [&](int j) {
         const int st = j & 1;
-        for (int ks = 0; ks < KS_QK; ++ks)
-          mma_ss(tmem + kColS + st * 128, sdesc_kmajor(q_addr, kBlk, ks),
-                 sdesc_kmajor(k_addr + st * L::kTile, kBlk, ks), idesc_qk, ks > 0);
+        issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc, ((st) ? k_desc_1 : k_desc_0), kBlk, kBlk,
+                                           idesc_qk, false);
         mma_commit(&s_full[st]);
         mma_commit(&k_empty[st]);
       };
@@ -194,9 +205,8 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
         ok = mbar_wait(&p_full, j & 1, ctx, kSitePFull, j);
         if (!ok) break;
         tc_fence_after();
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + kColO, tmem + kColS + st * 128 + ks * 8,
-                 sdesc_mnmajor(v_addr + st * L::kTile, kBlk, ks), idesc_pv, j > 0 || ks > 0);
+        issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, ((st) ? v_desc_1 : v_desc_0), kBlk, idesc_pv,
+                               j > 0);
         mma_commit(&v_empty[st]);
         mma_commit(&pv_done);
       }
@@ -204,36 +214,38 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
     __syncwarp();
   } else {
     // ------------------------------------------------------------------- softmax
-    const int r = tid;  // row of the tile, tensor-memory lane
-    const uint32_t lane_base = static_cast<uint32_t>(warp) * 32u;
-    float m_used = -INFINITY, l = 0.f;
+    // thread = (query row r, key half hf): 64 of the 128 scores of the row per block
+    const int r = (warp & 3) * 32 + lane;
+    const int hf = warp >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    uint64_t* pair_bar = &pair_bars[warp & 3];  // shared by warps w and w+4 (same rows)
+    float m_used = -INFINITY;             // running maximum, log2 domain
+    float l = 0.f;                        // partial row sum over this thread's keys
     bool ok = live;
-    uint32_t unit = 0;
+    uint32_t unit = BIAS == 1 ? hf : 0;  // 16-bit bias: units hf, hf+2, ...; byte mask: one per block
     for (int j = 0; j < nblk && ok; ++j) {
       const int st = j & 1;
-      const int n0 = j * 128;
+      const int n0 = j * 128 + hf * 64;  // first key of this thread's half
       ok = wait_warp(&s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
       tc_fence_after();
-      float s[128];
+      float s[64];
       {
         uint32_t* su = reinterpret_cast<uint32_t*>(s);
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-          tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + g * 32), su + g * 32);
+        tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 64), su);
+        tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 64 + 32), su + 32);
         tmem_ld_wait();
       }
-      // ---- scale, bias / mask
+      // ---- natural-domain score: q.k * sm_scale (+ bias) or -inf where masked
       if (BIAS == 0) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) s[i] *= p.scale_log2;
-      } else if (BIAS == 1) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u, ++unit) {
-          const int bs = unit & 3;
-          ok = wait_warp(&bias_full[bs], (unit >> 2) & 1, ctx, kSiteBiasFull, j);
-          if (!ok) break;
-          const uint8_t* tile = smem + L::kBias + bs * kBlk;
+        for (int i = 0; i < 64; ++i) s[i] *= p.sm_scale;
+      } else {
+        const int bs = unit % NB;
+        ok = wait_warp(&bias_full[bs], (unit / NB) & 1, ctx, kSiteBiasFull, j);
+        if (!ok) break;
+        const uint8_t* tile = smem + L::kBias + bs * kBlk;
+        if (BIAS == 1) {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, c));
@@ -241,56 +253,62 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 f = P2::unpack(w[e]);
-              const int i = u * 64 + c * 8 + e * 2;
-              s[i] = fmaf(s[i], p.scale_log2, f.x * kLog2e);
-              s[i + 1] = fmaf(s[i + 1], p.scale_log2, f.y * kLog2e);
+              s[c * 8 + e * 2] = fmaf(s[c * 8 + e * 2], p.sm_scale, f.x);
+              s[c * 8 + e * 2 + 1] = fmaf(s[c * 8 + e * 2 + 1], p.sm_scale, f.y);
             }
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bias_empty[bs]);
-        }
-        if (!ok) break;
-      } else {
-        const int bs = unit & 3;
-        ok = wait_warp(&bias_full[bs], (unit >> 2) & 1, ctx, kSiteBiasFull, j);
-        if (!ok) break;
-        const uint8_t* tile = smem + L::kBias + bs * kBlk;
+        } else {
+          // byte mask tile: [128 rows][128 bytes]; this half reads chunks 4*hf .. 4*hf+3
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, c));
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, hf * 4 + c));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 4; ++e) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int i = c * 16 + e * 4 + k;
-              const bool keep = ((w[e] >> (8 * k)) & 0xFFu) != 0;
-              s[i] = keep ? s[i] * p.scale_log2 : -INFINITY;
+              for (int k = 0; k < 4; ++k) {
+                const int i = c * 16 + e * 4 + k;
+                const bool keep = ((w[e] >> (8 * k)) & 0xFFu) != 0;
+                s[i] = keep ? s[i] * p.sm_scale : -INFINITY;
+              }
             }
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bias_empty[bs]);
-        ++unit;
+        unit += BIAS == 1 ? 2 : 1;
       }
       // ---- bounds and causal masks (only on blocks that need them)
-      {
+      if ((n0 + 64 > p.N) || (p.causal && n0 + 63 > m0)) {
         int limit = p.N - n0;
         if (p.causal) limit = min(limit, m0 + r - n0 + 1);
-        const bool block_needs = (n0 + 128 > p.N) || (p.causal && n0 + 127 > m0);
-        if (block_needs) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (i >= limit) s[i] = -INFINITY;
-        }
+        for (int i = 0; i < 64; ++i)
+          if (i >= limit) s[i] = -INFINITY;
       }
-      // ---- online softmax
-      float mx = s[0];
+      // ---- row maximum over this half, exchanged with the partner half
+      float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+      float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 12; i + 7 < 64; i += 8) {
+        mx0 = max3(mx0, s[i], s[i + 1]);
+        mx1 = max3(mx1, s[i + 2], s[i + 3]);
+        mx2 = max3(mx2, s[i + 4], s[i + 5]);
+        mx3 = max3(mx3, s[i + 6], s[i + 7]);
+      }
+      // 12 + 6*8 = 60 consumed; 60..63 left
+      mx0 = max3(mx0, s[60], s[61]);
+      mx1 = max3(mx1, s[62], s[63]);
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      xchg[j & 1][hf][r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair_bar);
+      ok = wait_warp(pair_bar, j & 1, ctx, kSitePair, j);
+      if (!ok) break;
+      mx = fmaxf(mx, xchg[j & 1][hf ^ 1][r]) * kLog2e;  // block maximum, log2 domain
       const bool need = mx > m_used + 8.0f;
       const bool any_need = __any_sync(0xffffffffu, need);
-      // P_{j} overwrites S_j; O may only be touched once P_{j-1} V_{j-1} has completed.
+      // O may only be touched once P_{j-1} V_{j-1} has completed.
       if (j > 0) {
         ok = wait_warp(&pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
         if (!ok) break;
@@ -303,29 +321,35 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
         if (j > 0) {
           tc_fence_after();
 #pragma unroll
-          for (int g = 0; g < DP / 32; ++g) {
+          for (int g = 0; g < kHalfD / 32; ++g) {
             uint32_t o[32];
-            tmem_ld32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+            tmem_ld32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+            tmem_st32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
           }
         }
       }
-      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
-      uint32_t pk[64];
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2(s[2 * i] - m_eff);
-        const float p1 = ex2(s[2 * i + 1] - m_eff);
-        sum += p0 + p1;
+      for (int i = 0; i < 32; i += 2) {
+        const float p0 = ex2(fmaf(s[2 * i], kLog2e, neg_m));
+        const float p1 = ex2(fmaf(s[2 * i + 1], kLog2e, neg_m));
+        const float p2 = ex2(fmaf(s[2 * i + 2], kLog2e, neg_m));
+        const float p3 = ex2(fmaf(s[2 * i + 3], kLog2e, neg_m));
+        sum0 += p0;
+        sum1 += p1;
+        sum2 += p2;
+        sum3 += p3;
         pk[i] = P2::pack(p0, p1);
+        pk[i + 1] = P2::pack(p2, p3);
       }
-      l += sum;
-      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128), pk);
-      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128 + 32), pk + 32);
+      l += (sum0 + sum1) + (sum2 + sum3);
+      // P (16 bit) over the S columns: this half's 64 keys -> 32 packed columns
+      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 32), pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -333,39 +357,41 @@ __global__ void __launch_bounds__(192, 1) fwd_kernel(const __grid_constant__ Fwd
     }
     // ---- epilogue: O / l -> global, log-sum-exp
     if (ok) ok = wait_warp(&pv_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
+    // full row sum = own half + partner half
     if (ok) {
+      xchg[nblk & 1][hf][r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair_bar);
+      ok = wait_warp(pair_bar, nblk & 1, ctx, kSitePair, nblk);
+    }
+    if (ok) {
+      l += xchg[nblk & 1][hf ^ 1][r];
       tc_fence_after();
       const int m = m0 + r;
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM +
                 h * p.o_sH;
 #pragma unroll
-      for (int g = 0; g < DP / 32; ++g) {
+      for (int g = 0; g < kHalfD / 32; ++g) {
         uint32_t o[32];
-        tmem_ld32(tmem_addr(tmem, lane_base, kColO + g * 32), o);
+        tmem_ld32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
         tmem_ld_wait();
         if (m < p.M) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            if (g * 32 + c * 8 < p.D) {
-              uint4 v;
-              v.x = P2::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
-              v.y = P2::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
-              v.z = P2::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
-              v.w = P2::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + g * 32 + c * 8) = v;
-            }
+            const int d = hf * kHalfD + g * 32 + c * 8;
+            if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + c * 8, inv);
           }
         }
       }
-      if (m < p.M)
+      if (hf == 0 && m < p.M)
         p.lse[(static_cast<int64_t>(bh)) * p.M + m] = l > 0.f ? m_used + log2f(l) : INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int DP, typename T, int BIAS>
@@ -381,7 +407,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 192, L::kDynamic, stream>>>(fp);
+  kern<<<grid, 320, L::kDynamic, stream>>>(fp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 
@@ -431,7 +457,7 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   fp.N = p.N;
   fp.D = p.D;
   fp.causal = p.causal ? 1 : 0;
-  fp.scale_log2 = p.sm_scale * kLog2e;
+  fp.sm_scale = p.sm_scale;
   const dim3 grid((p.M + 127) / 128, p.B * p.H);
   const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {

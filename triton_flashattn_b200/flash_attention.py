@@ -58,7 +58,7 @@ def _bias_ready(bias: torch.Tensor, elem_bytes: int) -> torch.Tensor:
     )
     if ok:
         return bias
-    align = 16 // elem_bytes
+    align = 32 // elem_bytes  # 32-byte pitch lets the kernels fetch whole sectors
     n_pad = (N + align - 1) // align * align
     buf = torch.empty((B, H, M, n_pad), dtype=bias.dtype, device=bias.device)
     out = buf[..., :N]
@@ -169,7 +169,7 @@ def _empty_dbias(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     No zero fill is needed: the dK/dV kernel writes every tile, including the
     causally skipped ones (the reference relies on zeros_like, FA:799)."""
     B, H, M, N = bias.shape
-    n_pad = (N + 7) // 8 * 8
+    n_pad = (N + 15) // 16 * 16
     buf = torch.empty((B, H, M, n_pad), dtype=dtype, device=bias.device)
     return buf[..., :N]
 
