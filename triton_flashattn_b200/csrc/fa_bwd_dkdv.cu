@@ -1,11 +1,12 @@
 // dK / dV (and dbias) kernel for sm_100a.
 //
 // One CTA owns 128 keys of one (batch, head) and walks the query blocks of 128
-// rows (only those at or below the diagonal when causal).  Roles (320 threads):
-//   warps 0-7  "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
-//              (query rows of the block) and on the 64-key column half (w>>2)
-//   warp 8     TMA producer (one lane): K, V once; Q ring (2), dO ring
-//   warp 9     MMA issuer (one lane), tensor-memory owner, bulk stores of dbias
+// rows (only those at or below the diagonal when causal).  Roles (576 threads):
+//   warps 0-15 "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
+//              (query rows of the block) and on the 32-key column quarter (w>>2)
+//   warp 16    TMA producer (one lane): K, V once; Q ring (2), dO ring
+//   warp 17    MMA issuer (one lane), tensor-memory owner
+//   warp 18    bulk tensor stores of the dS tile into dbias (one lane)
 // Per query block t:
 //   S  = Q_t K^T            (tensor memory, 128 columns)
 //   dP = dO_t V^T           (tensor memory, 128 columns)
@@ -14,8 +15,8 @@
 //   dV += P^T dO_t          (sP and dO_t consumed MN-major)
 //   dK += dS^T Q_t          (sDS and Q_t consumed MN-major)
 //   dbias[b,h,m-block,n-block] <- sDS  (one bulk tensor store of the same tile)
-// The bias never touches shared memory: every row thread fetches its own 128
-// contiguous bytes (64 keys) with 128-bit loads one query block ahead.
+// The bias never touches shared memory: every row thread fetches its own 64
+// contiguous bytes (32 keys) with 256-bit loads one query block ahead.
 // Causally skipped tiles of dbias are written as zeros by this kernel, so dbias
 // needs no prior fill.
 //
@@ -25,6 +26,12 @@
 #include "fa_host.cuh"
 
 namespace fa {
+#ifdef FA_TRACE
+__device__ long long g_fa_trace_dkdv[8192];
+#define TR(role, step, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 16) g_fa_trace_dkdv[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TR(role, step, slot) do {} while (0)
+#endif
 namespace {
 
 struct DkdvParams {
@@ -33,6 +40,7 @@ struct DkdvParams {
   CUtensorMap map_v;
   CUtensorMap map_do;
   CUtensorMap map_dbias;
+  CUtensorMap map_bias;  // only used to prefetch bias tiles into L2
   const void* bias;
   void* dk;
   void* dv;
@@ -42,7 +50,7 @@ struct DkdvParams {
   int64_t bias_sB, bias_sH, bias_sM;
   int64_t dk_sB, dk_sN, dk_sH, dv_sB, dv_sN, dv_sH;
   int H, M, N, D;
-  int causal, write_dbias, bias_vec32;
+  int causal, write_dbias, bias_vec32, bias_b_mul, bias_h_mul;
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
 };
@@ -66,7 +74,7 @@ struct DkdvSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ DkdvParams p) {
+__global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ DkdvParams p) {
   using L = DkdvSmem<DP>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;
@@ -109,17 +117,17 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&p_ready, 8);
-    mbar_init(&ds_ready, 8);
+    mbar_init(&p_ready, 16);
+    mbar_init(&ds_ready, 16);
     mbar_init(&dv_done, 1);
     mbar_init(&dk_done, 1);
     mbar_init(&st_done, 1);
-    mbar_init(&zero_ready, 8);
-    mbar_init(&s_free, 8);
-    mbar_init(&dp_free, 8);
+    mbar_init(&zero_ready, 16);
+    mbar_init(&s_free, 16);
+    mbar_init(&dp_free, 16);
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -129,7 +137,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
   const uint32_t tmem = tmem_slot;
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && live && T_steps > 0) {
       tma_prefetch_desc(&p.map_q);
@@ -142,9 +150,24 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
       }
       bool ok = true;
+      constexpr int kBiasAhead = 2;  // bias tiles are pulled into L2 this many steps early
+      if (BIAS != 0) {
+        for (int t = 0; t < kBiasAhead && t < T_steps; ++t) {
+          const int mp = (i_start + t) * 128;
+          tma_prefetch_l2_4d(&p.map_bias, n0, mp, h * p.bias_h_mul, b * p.bias_b_mul);
+          if (BIAS == 1 && n0 + 64 < p.N)
+            tma_prefetch_l2_4d(&p.map_bias, n0 + 64, mp, h * p.bias_h_mul, b * p.bias_b_mul);
+        }
+      }
       for (int t = 0; t < T_steps && ok; ++t) {
         const int m0 = (i_start + t) * 128;
         const int qs = t & 1;
+        if (BIAS != 0 && t + kBiasAhead < T_steps) {
+          const int mp = (i_start + t + kBiasAhead) * 128;
+          tma_prefetch_l2_4d(&p.map_bias, n0, mp, h * p.bias_h_mul, b * p.bias_b_mul);
+          if (BIAS == 1 && n0 + 64 < p.N)
+            tma_prefetch_l2_4d(&p.map_bias, n0 + 64, mp, h * p.bias_h_mul, b * p.bias_b_mul);
+        }
         if (t >= 2) ok = mbar_wait(&q_empty[qs], ((t >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
         if (!ok) break;
         mbar_expect_tx(&q_full[qs], L::kTile);
@@ -161,7 +184,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
                       h, m0, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
@@ -171,21 +194,6 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
       const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDs);
       bool ok = true;
-      // zero tiles of dbias above the diagonal (store "phase 0")
-      if (p.write_dbias && p.causal) {
-        ok = mbar_wait(&zero_ready, 0, ctx, kSiteZeroReady, 0);
-        if (ok) {
-          const int nz = min(nb, n_mblk);
-          for (int i = 0; i < nz; ++i) {
-            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
-            if (n0 + 64 < p.N)
-              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
-          }
-          tma_store_commit();
-          tma_store_wait_read<0>();
-        }
-      }
-      mbar_arrive(&st_done);
       // slice-0 descriptors: K-major views (S, dP) and MN-major views (dV, dK)
       const uint64_t k_km = make_sdesc(k_addr, 0, 1024), v_km = make_sdesc(v_addr, 0, 1024);
       const uint64_t q_km_0 = make_sdesc(q_addr, 0, 1024), q_km_1 = make_sdesc(q_addr + L::kTile, 0, 1024);
@@ -219,47 +227,80 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         const int qs = t & 1;
         const int ds = t % kDoStages;
         // S of the next block as soon as the row threads hold S_t in registers
+        TR(1, t, 0);
         if (t + 1 < T_steps) {
           ok = mbar_wait(&s_free, t & 1, ctx, kSiteSFree, t);
+          TR(1, t, 1);
           if (ok) ok = mbar_wait(&q_full[(t + 1) & 1], ((t + 1) >> 1) & 1, ctx, kSiteQFull, t + 1);
           if (!ok) break;
+          TR(1, t, 2);
           tc_fence_after();
           issue_s(t + 1);
+          TR(1, t, 3);
         }
         // dV += P^T dO
         ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
         if (!ok) break;
+        TR(1, t, 4);
         tc_fence_after();
         issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ((ds) ? do_mn_1 : do_mn_0), kBlk, kBlk, idesc_g, t > 0);
         mma_commit(&do_empty[ds]);
         mma_commit(&dv_done);
-        // the bulk store of dS_{t-1} must have finished reading sDS before dS_t is written
-        if (t >= 1) {
-          if (p.write_dbias) tma_store_wait_read<0>();
-          mbar_arrive(&st_done);
-        }
+        TR(1, t, 5);
         // dK += dS^T Q
+        TR(1, t, 6);
         ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
         if (!ok) break;
+        TR(1, t, 7);
         tc_fence_after();
         issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, ((qs) ? q_mn_1 : q_mn_0), kBlk, kBlk, idesc_g, t > 0);
         mma_commit(&q_empty[qs]);
         mma_commit(&dk_done);
-        if (p.write_dbias) {
-          const int m0 = (i_start + t) * 128;
-          tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
-          if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
-          tma_store_commit();
-        }
+        TR(1, t, 8);
         // dP of the next block (its columns were handed back before dS_t was written)
         if (t + 1 < T_steps) {
           const int ds1 = (t + 1) % kDoStages;
           ok = mbar_wait(&dp_free, t & 1, ctx, kSiteDpFree, t);
+          TR(1, t, 9);
           if (ok) ok = mbar_wait(&do_full[ds1], ((t + 1) / kDoStages) & 1, ctx, kSiteDoFull, t + 1);
           if (!ok) break;
+          TR(1, t, 10);
           tc_fence_after();
           issue_dp(t + 1);
+          TR(1, t, 11);
         }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 18) {
+    // ------------------------------------------------------------- dbias stores
+    // phase 0 of st_done: zero tiles above the diagonal are out (or nothing to do);
+    // phase t+1: the store of dS_t has finished reading sDS.
+    if (lane == 0 && live && p.write_dbias) {
+      bool ok = true;
+      if (p.causal) {
+        ok = mbar_wait(&zero_ready, 0, ctx, kSiteZeroReady, 0);
+        if (ok) {
+          const int nz = min(nb, n_mblk);
+          for (int i = 0; i < nz; ++i) {
+            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
+            if (n0 + 64 < p.N)
+              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
+          }
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+      }
+      mbar_arrive(&st_done);
+      for (int t = 0; t < T_steps && ok; ++t) {
+        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
+        if (!ok) break;
+        const int m0 = (i_start + t) * 128;
+        tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
+        if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
+        tma_store_commit();
+        tma_store_wait_read<0>();
+        mbar_arrive(&st_done);
       }
       tma_store_wait_all<0>();
     }
@@ -267,32 +308,34 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
   } else {
     // --------------------------------------------------------------- row threads
     const int r = (warp & 3) * 32 + lane;  // query row inside the block = tensor-memory lane
-    const int hf = warp >> 2;              // column half: keys n0 + 64*hf .. +63
+    const int qt = warp >> 2;              // column quarter: keys n0 + 32*qt .. +31
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     bool ok = live;
-    uint8_t* sP = smem + L::kP + hf * kBlk;
-    uint8_t* sDS = smem + L::kDs + hf * kBlk;
+    // this thread's four 16-byte chunks inside the [128][128] 16-bit tiles
+    uint8_t* sP = smem + L::kP + (qt >> 1) * kBlk;
+    uint8_t* sDS = smem + L::kDs + (qt >> 1) * kBlk;
+    const int chunk0 = (qt & 1) * 4;
 
     if (p.write_dbias && p.causal && ok) {
       // zero tile for the causally skipped part of dbias
       uint4* z = reinterpret_cast<uint4*>(smem + L::kDs);
-      for (int i = tid; i < 2 * kBlk / 16; i += 256) z[i] = make_uint4(0, 0, 0, 0);
+      for (int i = tid; i < 2 * kBlk / 16; i += 512) z[i] = make_uint4(0, 0, 0, 0);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&zero_ready);
     }
 
-    const int col0 = n0 + hf * 64;
+    const int col0 = n0 + qt * 32;
     const int64_t bias_bh = b * p.bias_sB + h * p.bias_sH;
     BiasRegs<BIAS> bnext;
-    float lse_next = -INFINITY, delta_next = 0.f;  // lse_next holds -LSE2 of the row
+    float lse_next = INFINITY, delta_next = 0.f;
     auto prefetch = [&](int t) {
       const int m = (i_start + t) * 128 + r;
       const bool row_ok = m < p.M;
       if (BIAS != 0)
         load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N,
-                             p.bias_vec32 != 0);
-      lse_next = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
+                            p.bias_vec32 != 0);
+      lse_next = row_ok ? __ldg(p.lse + (int64_t)bh * p.M + m) : INFINITY;
       delta_next = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
     };
     if (ok && T_steps > 0) prefetch(0);
@@ -300,27 +343,26 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     for (int t = 0; t < T_steps && ok; ++t) {
       const int m0 = (i_start + t) * 128;
       BiasRegs<BIAS> bcur = bnext;
-      const float neg_lse = lse_next, delta_r = delta_next;
+      const float lse_cur = lse_next, delta_r = delta_next;
       if (t + 1 < T_steps) prefetch(t + 1);
 
       // ---- P
+      if (tid == 0) TR(0, t, 0);
       ok = wait_warp(&s_full, t & 1, ctx, kSiteSFull, t);
       if (!ok) break;
+      if (tid == 0) TR(0, t, 1);
       tc_fence_after();
-      float pr[64];
-      {
-        uint32_t* su = reinterpret_cast<uint32_t*>(pr);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64), su);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64 + 32), su + 32);
-        tmem_ld_wait();
-      }
+      float pr[32];
+      tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
+      tmem_ld_wait();
       // S_t now lives in registers: hand its columns back for S_{t+1}
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free);
-      // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have -LSE2 = -inf
+      // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
+      const float neg_lse = -lse_cur;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < 32; ++i) {
         if (BIAS == 1) {
           const float2 f = P2::unpack(bcur.w[i >> 1]);
           pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
@@ -331,66 +373,73 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
           pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
         }
       }
-      if ((col0 + 64 > p.N) || (p.causal && col0 + 63 > m0)) {
+      if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
         int limit = p.N - col0;
         if (p.causal) limit = min(limit, m0 + r - col0 + 1);
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (i >= limit) pr[i] = 0.f;
       }
+      if (tid == 0) TR(0, t, 2);
       if (t >= 1) {
         ok = wait_warp(&dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
         if (!ok) break;
       }
+      if (tid == 0) TR(0, t, 3);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 v;
         v.x = P2::pack(pr[c * 8 + 0], pr[c * 8 + 1]);
         v.y = P2::pack(pr[c * 8 + 2], pr[c * 8 + 3]);
         v.z = P2::pack(pr[c * 8 + 4], pr[c * 8 + 5]);
         v.w = P2::pack(pr[c * 8 + 6], pr[c * 8 + 7]);
-        *reinterpret_cast<uint4*>(sP + swz_off(r, c)) = v;
+        *reinterpret_cast<uint4*>(sP + swz_off(r, chunk0 + c)) = v;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
+      if (tid == 0) TR(0, t, 4);
 
       // ---- dS
       ok = wait_warp(&dp_full, t & 1, ctx, kSiteDpFull, t);
       if (!ok) break;
+      if (tid == 0) TR(0, t, 5);
       tc_fence_after();
-      uint32_t dsu[32];
+      uint32_t dsu[16];
       {
         uint32_t dp[32];
+        tmem_ld32(tmem_addr(tmem, lane_base, kColDp + qt * 32), dp);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dp_free);
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          tmem_ld32(tmem_addr(tmem, lane_base, kColDp + hf * 64 + g * 32), dp);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float d0 = pr[g * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
-            const float d1 = pr[g * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
-            dsu[g * 16 + i] = P2::pack(d0, d1);
-          }
+        for (int i = 0; i < 16; ++i) {
+          const float d0 = pr[2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
+          const float d1 = pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
+          dsu[i] = P2::pack(d0, d1);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&dp_free);
+      if (tid == 0) TR(0, t, 6);
       if (t >= 1) {
         ok = wait_warp(&dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
         if (!ok) break;
       }
-      ok = wait_warp(&st_done, t & 1, ctx, kSiteStDone, t);
-      if (!ok) break;
+      if (tid == 0) TR(0, t, 7);
+      if (p.write_dbias) {
+        ok = wait_warp(&st_done, t & 1, ctx, kSiteStDone, t);
+        if (!ok) break;
+      }
+      if (tid == 0) TR(0, t, 8);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + swz_off(r, c)) = v;
+        *reinterpret_cast<uint4*>(sDS + swz_off(r, chunk0 + c)) = v;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready);
+      if (tid == 0) TR(0, t, 9);
     }
 
     // ---- epilogue: dV, dK (rows = keys) -> global
@@ -401,8 +450,8 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
     if (ok) {
       tc_fence_after();
       const int n = n0 + r;
-      constexpr int kHalfCols = DP / 2;  // columns of the head dim this thread stores
-      const int d0 = hf * kHalfCols;
+      constexpr int kQD = DP / 4;  // columns of the head dim this thread stores (16 or 32)
+      const int d0 = qt * kQD;
       T* dkrow = reinterpret_cast<T*>(p.dk) + b * p.dk_sB + (int64_t)n * p.dk_sN + h * p.dk_sH;
       T* dvrow = reinterpret_cast<T*>(p.dv) + b * p.dv_sB + (int64_t)n * p.dv_sN + h * p.dv_sH;
 #pragma unroll
@@ -410,29 +459,19 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
         T* row = which == 0 ? dvrow : dkrow;
         const uint32_t colbase = which == 0 ? kColDv : kColDk;
         const float mul = which == 0 ? 1.0f : p.sm_scale;
+        uint32_t a[kQD];
+        if (T_steps > 0) {
+          tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, colbase + d0), a);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int g = 0; g < kHalfCols / 32; ++g) {
-          uint32_t a[32];
-          if (T_steps > 0) {
-            tmem_ld32(tmem_addr(tmem, lane_base, colbase + d0 + g * 32), a);
-            tmem_ld_wait();
-          } else {
+          for (int i = 0; i < kQD; ++i) a[i] = 0;
+        }
+        if (n < p.N) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) a[i] = 0;
-          }
-          if (n < p.N) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int d = d0 + g * 32 + c * 8;
-              if (d < p.D) {
-                uint4 v;
-                v.x = P2::pack(__uint_as_float(a[c * 8 + 0]) * mul, __uint_as_float(a[c * 8 + 1]) * mul);
-                v.y = P2::pack(__uint_as_float(a[c * 8 + 2]) * mul, __uint_as_float(a[c * 8 + 3]) * mul);
-                v.z = P2::pack(__uint_as_float(a[c * 8 + 4]) * mul, __uint_as_float(a[c * 8 + 5]) * mul);
-                v.w = P2::pack(__uint_as_float(a[c * 8 + 6]) * mul, __uint_as_float(a[c * 8 + 7]) * mul);
-                *reinterpret_cast<uint4*>(row + d) = v;
-              }
-            }
+          for (int c = 0; c < kQD / 8; ++c) {
+            const int d = d0 + c * 8;
+            if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, mul);
           }
         }
       }
@@ -441,7 +480,7 @@ __global__ void __launch_bounds__(320, 1) dkdv_kernel(const __grid_constant__ Dk
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 17) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int DP, typename T, int BIAS>
@@ -457,7 +496,7 @@ int launch_inst(const DkdvParams& kp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 320, L::kDynamic, stream>>>(kp);
+  kern<<<grid, 608, L::kDynamic, stream>>>(kp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 
@@ -472,6 +511,13 @@ int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t str
 }
 
 }  // namespace
+
+#ifdef FA_TRACE
+extern "C" int fa_debug_read_trace_dkdv(long long* out, int n) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out, g_fa_trace_dkdv, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   DkdvParams kp;
@@ -496,6 +542,17 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
     return reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || s[0] % 8 || s[1] % 8 || s[2] % 8;
   };
   if (bad(p.dk, p.dk_stride) || bad(p.dv, p.dv_stride)) return FA_ERR_ALIGN;
+  kp.bias_b_mul = kp.bias_h_mul = 0;
+  kp.map_bias = kp.map_q;
+  if (p.bias_kind == FA_BIAS_SAME) {
+    r = make_tmap_bhmn(&kp.map_bias, p.bias, 2, p.B, p.H, p.M, p.N, p.bias_stride, 64, 128,
+                       &kp.bias_b_mul, &kp.bias_h_mul);
+    if (r) return r;
+  } else if (p.bias_kind == FA_BIAS_BOOL) {
+    r = make_tmap_bhmn(&kp.map_bias, p.bias, 1, p.B, p.H, p.M, p.N, p.bias_stride, 128, 128,
+                       &kp.bias_b_mul, &kp.bias_h_mul);
+    if (r) return r;
+  }
   if (p.bias_kind != FA_BIAS_NONE) {
     const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
     if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || (p.bias_stride[0] * eb) % 16 ||

@@ -2,8 +2,8 @@
 //
 // (1) dq_recompute_kernel -- general path (no bias, bool mask, float bias).
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks.
-// Roles (320 threads): warps 0-7 row threads (lanes 32*(w&3).., key half w>>2),
-// warp 8 TMA producer, warp 9 MMA issuer and tensor-memory owner.  Per key block:
+// Roles (576 threads): warps 0-15 row threads (lanes 32*(w&3).., key quarter w>>2),
+// warp 16 TMA producer, warp 17 MMA issuer and tensor-memory owner.  Per key block:
 //   S  = Q K_j^T, dP = dO V_j^T   (tensor memory)
 //   row threads: P = exp2(S*scale*log2e + bias*log2e - LSE2); dS = P*(dP - delta)
 //                -> 16-bit tile sDS in shared memory
@@ -61,7 +61,7 @@ struct DqSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_constant__ DqParams p) {
+__global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_constant__ DqParams p) {
   using L = DqSmem<DP>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;
@@ -101,13 +101,13 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&s_free, 8);
-    mbar_init(&dp_free, 8);
-    mbar_init(&ds_ready, 8);
+    mbar_init(&s_free, 16);
+    mbar_init(&dp_free, 16);
+    mbar_init(&ds_ready, 16);
     mbar_init(&dq_done, 1);
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
   const uint32_t tmem = tmem_slot;
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && live) {
       tma_prefetch_desc(&p.map_q);
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
                       n0, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
@@ -210,20 +210,22 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
   } else {
     // --------------------------------------------------------------- row threads
     const int r = (warp & 3) * 32 + lane;
-    const int hf = warp >> 2;
+    const int qt = warp >> 2;  // key quarter of every block
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     const int m = m0 + r;
     const bool row_ok = m < p.M;
     bool ok = live;
-    uint8_t* sDS = smem + L::kDs + hf * kBlk;
+    uint8_t* sDS = smem + L::kDs + (qt >> 1) * kBlk;
+    const int chunk0 = (qt & 1) * 4;
     const int64_t bias_row = b * p.bias_sB + h * p.bias_sH + (int64_t)m * p.bias_sM;
     const float neg_lse = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
     const float delta_r = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
     BiasRegs<BIAS> bnext;
-    if (ok && BIAS != 0) load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, hf * 64, p.N, p.bias_vec32 != 0);
+    if (ok && BIAS != 0)
+      load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, qt * 32, p.N, p.bias_vec32 != 0);
 
     for (int j = 0; j < nblk && ok; ++j) {
-      const int col0 = j * 128 + hf * 64;
+      const int col0 = j * 128 + qt * 32;
       BiasRegs<BIAS> bcur = bnext;
       if (BIAS != 0 && j + 1 < nblk)
         load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, col0 + 128, p.N, p.bias_vec32 != 0);
@@ -231,19 +233,15 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
       ok = wait_warp(&s_full, j & 1, ctx, kSiteSFull, j);
       if (!ok) break;
       tc_fence_after();
-      float pr[64];
-      {
-        uint32_t* su = reinterpret_cast<uint32_t*>(pr);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64), su);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + hf * 64 + 32), su + 32);
-        tmem_ld_wait();
-      }
+      float pr[32];
+      tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free);
 
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < 32; ++i) {
         if (BIAS == 1) {
           const float2 f = P2::unpack(bcur.w[i >> 1]);
           pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
@@ -254,43 +252,40 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
           pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
         }
       }
-      if ((col0 + 64 > p.N) || (p.causal && col0 + 63 > m0)) {
+      if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
         int limit = p.N - col0;
         if (p.causal) limit = min(limit, m - col0 + 1);
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (i >= limit) pr[i] = 0.f;
       }
 
       ok = wait_warp(&dp_full, j & 1, ctx, kSiteDpFull, j);
       if (!ok) break;
       tc_fence_after();
-      uint32_t dsu[32];
+      uint32_t dsu[16];
       {
         uint32_t dp[32];
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          tmem_ld32(tmem_addr(tmem, lane_base, kColDp + hf * 64 + g * 32), dp);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float d0 = pr[g * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
-            const float d1 = pr[g * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
-            dsu[g * 16 + i] = P2::pack(d0, d1);
-          }
-        }
+        tmem_ld32(tmem_addr(tmem, lane_base, kColDp + qt * 32), dp);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&dp_free);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float d0 = pr[2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
+          const float d1 = pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
+          dsu[i] = P2::pack(d0, d1);
+        }
       }
       if (j >= 1) {
         ok = wait_warp(&dq_done, (j - 1) & 1, ctx, kSiteDqDone, j);
         if (!ok) break;
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + swz_off(r, c)) = v;
+        *reinterpret_cast<uint4*>(sDS + swz_off(r, chunk0 + c)) = v;
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -300,20 +295,17 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
     if (ok) ok = wait_warp(&dq_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
     if (ok) {
       tc_fence_after();
-      constexpr int kHalfCols = DP / 2;
-      const int d0 = hf * kHalfCols;
+      constexpr int kQD = DP / 4;
+      const int d0 = qt * kQD;
       T* row = reinterpret_cast<T*>(p.dq) + b * p.dq_sB + (int64_t)m * p.dq_sM + h * p.dq_sH;
+      uint32_t a[kQD];
+      tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColDq + d0), a);
+      tmem_ld_wait();
+      if (row_ok) {
 #pragma unroll
-      for (int g = 0; g < kHalfCols / 32; ++g) {
-        uint32_t a[32];
-        tmem_ld32(tmem_addr(tmem, lane_base, kColDq + d0 + g * 32), a);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int d = d0 + g * 32 + c * 8;
-            if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, p.sm_scale);
-          }
+        for (int c = 0; c < kQD / 8; ++c) {
+          const int d = d0 + c * 8;
+          if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, p.sm_scale);
         }
       }
     }
@@ -321,7 +313,7 @@ __global__ void __launch_bounds__(320, 1) dq_recompute_kernel(const __grid_const
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 17) tmem_dealloc(tmem, kTmemCols);
 }
 
 // ----------------------------------------------------------------------------
@@ -469,7 +461,7 @@ int launch_recompute(const DqParams& kp, dim3 grid, cudaStream_t stream) {
   static bool configured[64] = {};
   auto kern = dq_recompute_kernel<DP, T, BIAS>;
   if (int r = configure(kern, L::kDynamic, configured)) return r;
-  kern<<<grid, 320, L::kDynamic, stream>>>(kp);
+  kern<<<grid, 576, L::kDynamic, stream>>>(kp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 

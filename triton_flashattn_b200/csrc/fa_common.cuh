@@ -174,6 +174,15 @@ __device__ __forceinline__ void tma_load_4d_hint(void* smem_dst, const CUtensorM
       : "memory");
 }
 
+// Asks the TMA unit to pull a tile into L2 only (no shared-memory destination).
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2,
+                                                   int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0,
                                              int c1, int c2, int c3) {
   asm volatile(
@@ -271,6 +280,23 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
       "r"(r[30]), "r"(r[31])
       : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// NC (16 or 32) consecutive columns
+template <int NC>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  if (NC == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+}
+template <int NC>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  if (NC == 32) tmem_st32(taddr, r); else tmem_st16(taddr, r);
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -470,22 +496,22 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, const 
   return __all_sync(0xffffffffu, ok);
 }
 
-// 64 bias values of one row half, as raw 16-bit pairs (BIAS == 1) or bytes (BIAS == 2).
+// 32 bias values of one row quarter, as raw 16-bit pairs (BIAS == 1) or bytes (BIAS == 2).
 template <int BIAS>
 struct BiasRegs {
-  uint32_t w[BIAS == 1 ? 32 : (BIAS == 2 ? 16 : 1)];
+  uint32_t w[BIAS == 1 ? 16 : (BIAS == 2 ? 8 : 1)];
 };
 
-// Reads bias[row][col0 .. col0+63] straight from global memory; out-of-range elements
+// Reads bias[row][col0 .. col0+31] straight from global memory; out-of-range elements
 // read as zero.  `vec32` (uniform): rows are 32-byte aligned, so whole sectors are
 // fetched with 256-bit loads; otherwise 128-bit loads; element-wise at a ragged edge.
 template <int BIAS>
 __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bias_base,
                                               int64_t row_off, bool row_ok, int col0, int N,
                                               bool vec32) {
-  constexpr int kElem = BIAS == 1 ? 2 : 1;        // bytes per element
-  constexpr int kWords = BIAS == 1 ? 32 : 16;     // 32-bit words per 64 elements
-  constexpr int kPerWord = 4 / kElem;             // elements per word
+  constexpr int kElem = BIAS == 1 ? 2 : 1;     // bytes per element
+  constexpr int kWords = BIAS == 1 ? 16 : 8;   // 32-bit words per 32 elements
+  constexpr int kPerWord = 4 / kElem;          // elements per word
   if (BIAS == 0) return;
   const uint8_t* rowp = reinterpret_cast<const uint8_t*>(bias_base) + row_off * kElem;
   if (!row_ok || col0 >= N) {
@@ -493,7 +519,7 @@ __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bi
     for (int i = 0; i < kWords; ++i) br.w[i] = 0;
     return;
   }
-  if (col0 + 64 <= N) {
+  if (col0 + 32 <= N) {
     if (vec32) {
 #pragma unroll
       for (int c = 0; c < kWords / 8; ++c) ldg256(rowp + (col0 * kElem) + c * 32, br.w + c * 8);

@@ -1,12 +1,12 @@
 // Forward attention kernel for sm_100a.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
-// 128 keys.  Roles (320 threads):
-//   warps 0-7  softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
-//              lanes) and the 64-key half (w>>2) of every block; the two halves of
-//              a row exchange their partial maxima through shared memory
-//   warp 8     TMA producer (one elected lane): Q once, K / V rings, bias ring
-//   warp 9     MMA issuer (one lane) and tensor-memory owner
+// 128 keys.  Roles (576 threads):
+//   warps 0-15 softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
+//              lanes) and the 32-key quarter (w>>2) of every block; the four
+//              quarters of a row exchange partial maxima through shared memory
+//   warp 16    TMA producer (one elected lane): Q once, K / V rings, bias ring
+//   warp 17    MMA issuer (one lane) and tensor-memory owner
 // Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
 // in tensor memory, double buffered) -> softmax threads read S_j, add the bias
 // tile (streamed by TMA into a shared-memory ring), apply masks, run the online
@@ -24,6 +24,12 @@
 #include "fa_host.cuh"
 
 namespace fa {
+#ifdef FA_TRACE
+__device__ long long g_fa_trace[8192];
+#define TR(role, step, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 16) g_fa_trace[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TR(role, step, slot) do {} while (0)
+#endif
 namespace {
 
 struct FwdParams {
@@ -58,12 +64,12 @@ struct FwdSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
   constexpr int KS_QK = DP / 16; // MMA K slices of Q K^T
-  constexpr int kHalfD = DP / 2; // output columns handled by one softmax thread
+  constexpr int kQD = DP / 4;    // output columns handled by one softmax thread (16 or 32)
   constexpr uint32_t NB = L::kBiasStages > 0 ? L::kBiasStages : 1;
   constexpr uint32_t kColS = 0, kColO = 256;
   constexpr uint32_t kTmemCols = 512;
@@ -73,8 +79,8 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full,
       pv_done;
-  __shared__ uint64_t bias_full[4], bias_empty[4], pair_bars[4];
-  __shared__ float xchg[2][2][128];  // [step parity][column half][row]: partial row maxima / sums
+  __shared__ uint64_t bias_full[4], bias_empty[4], row_bars[4];
+  __shared__ float xchg[2][4][128];  // [step parity][key quarter][row]: partial row maxima / sums
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -102,16 +108,16 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    mbar_init(&p_full, 8);
+    mbar_init(&p_full, 16);
     mbar_init(&pv_done, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bias_full[i], 1);
-      mbar_init(&bias_empty[i], BIAS == 2 ? 8 : 4);
-      mbar_init(&pair_bars[i], 2);
+      mbar_init(&bias_empty[i], BIAS == 2 ? 16 : 8);
+      mbar_init(&row_bars[i], 4);
     }
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
   // A kernel launched after an earlier one recorded an error does no work.
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && live) {
       tma_prefetch_desc(&p.map_q);
@@ -167,7 +173,7 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
                       n0, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
@@ -194,52 +200,66 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
       }
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j & 1;
+        TR(1, j, 0);
         if (j + 1 < nblk) {
           ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, kSiteKFull, j + 1);
           if (!ok) break;
+          TR(1, j, 1);
           tc_fence_after();
           issue_qk(j + 1);
+          TR(1, j, 2);
         }
         ok = mbar_wait(&v_full[st], (j >> 1) & 1, ctx, kSiteVFull, j);
         if (!ok) break;
+        TR(1, j, 3);
         ok = mbar_wait(&p_full, j & 1, ctx, kSitePFull, j);
         if (!ok) break;
+        TR(1, j, 4);
         tc_fence_after();
         issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, ((st) ? v_desc_1 : v_desc_0), kBlk, idesc_pv,
                                j > 0);
         mma_commit(&v_empty[st]);
         mma_commit(&pv_done);
+        TR(1, j, 5);
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------- softmax
-    // thread = (query row r, key half hf): 64 of the 128 scores of the row per block
+    // thread = (query row r, key quarter qt): 32 of the 128 scores of the row per block
     const int r = (warp & 3) * 32 + lane;
-    const int hf = warp >> 2;
+    const int qt = warp >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
-    uint64_t* pair_bar = &pair_bars[warp & 3];  // shared by warps w and w+4 (same rows)
-    float m_used = -INFINITY;             // running maximum, log2 domain
-    float l = 0.f;                        // partial row sum over this thread's keys
+    uint64_t* row_bar = &row_bars[warp & 3];  // shared by the four warps that own the same rows
+    float m_used = -INFINITY;                 // running maximum, log2 domain
+    float l = 0.f;                            // partial row sum over this thread's keys
     bool ok = live;
-    uint32_t unit = BIAS == 1 ? hf : 0;  // 16-bit bias: units hf, hf+2, ...; byte mask: one per block
+    const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
+    const float scale_log2 = p.sm_scale * kLog2e;
+    uint32_t unit = BIAS == 1 ? (qt >> 1) : 0;  // 16-bit bias: units hf, hf+2, ...; mask: one per block
     for (int j = 0; j < nblk && ok; ++j) {
       const int st = j & 1;
-      const int n0 = j * 128 + hf * 64;  // first key of this thread's half
+      const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
+      if (tid == 0) TR(0, j, 0);
       ok = wait_warp(&s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
+      if (tid == 0) TR(0, j, 1);
       tc_fence_after();
-      float s[64];
-      {
-        uint32_t* su = reinterpret_cast<uint32_t*>(s);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 64), su);
-        tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 64 + 32), su + 32);
-        tmem_ld_wait();
-      }
-      // ---- natural-domain score: q.k * sm_scale (+ bias) or -inf where masked
+      float s[32];
+      tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 32), reinterpret_cast<uint32_t*>(s));
+      tmem_ld_wait();
+      if (tid == 0) TR(0, j, 2);
+      // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
+      // Without a bias (and a positive scale) the raw q.k is kept and the scale is
+      // folded into the exponent below.
+      float mul = kLog2e;  // exponent = s * mul - m
       if (BIAS == 0) {
+        if (fold_scale) {
+          mul = scale_log2;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) s[i] *= p.sm_scale;
+          for (int i = 0; i < 32; ++i) s[i] *= p.sm_scale;
+        }
       } else {
         const int bs = unit % NB;
         ok = wait_warp(&bias_full[bs], (unit / NB) & 1, ctx, kSiteBiasFull, j);
@@ -247,8 +267,8 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
         const uint8_t* tile = smem + L::kBias + bs * kBlk;
         if (BIAS == 1) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, c));
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, (qt & 1) * 4 + c));
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -258,10 +278,10 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
             }
           }
         } else {
-          // byte mask tile: [128 rows][128 bytes]; this half reads chunks 4*hf .. 4*hf+3
+          // byte mask tile: [128 rows][128 bytes]; this quarter reads chunks 2*qt, 2*qt+1
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, hf * 4 + c));
+          for (int c = 0; c < 2; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, qt * 2 + c));
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -279,33 +299,36 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
         unit += BIAS == 1 ? 2 : 1;
       }
       // ---- bounds and causal masks (only on blocks that need them)
-      if ((n0 + 64 > p.N) || (p.causal && n0 + 63 > m0)) {
+      if ((n0 + 32 > p.N) || (p.causal && n0 + 31 > m0)) {
         int limit = p.N - n0;
         if (p.causal) limit = min(limit, m0 + r - n0 + 1);
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (i >= limit) s[i] = -INFINITY;
       }
-      // ---- row maximum over this half, exchanged with the partner half
+      if (tid == 0) TR(0, j, 3);
+      // ---- row maximum over this quarter, exchanged with the three partner quarters
       float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
       float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-      for (int i = 12; i + 7 < 64; i += 8) {
+      for (int i = 12; i + 7 < 32; i += 8) {
         mx0 = max3(mx0, s[i], s[i + 1]);
         mx1 = max3(mx1, s[i + 2], s[i + 3]);
         mx2 = max3(mx2, s[i + 4], s[i + 5]);
         mx3 = max3(mx3, s[i + 6], s[i + 7]);
       }
-      // 12 + 6*8 = 60 consumed; 60..63 left
-      mx0 = max3(mx0, s[60], s[61]);
-      mx1 = max3(mx1, s[62], s[63]);
+      mx0 = max3(mx0, s[28], s[29]);  // 12 + 2*8 = 28 consumed; 28..31 left
+      mx1 = max3(mx1, s[30], s[31]);
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      xchg[j & 1][hf][r] = mx;
+      if (tid == 0) TR(0, j, 4);
+      xchg[j & 1][qt][r] = mx;
       __syncwarp();
-      if (lane == 0) mbar_arrive(pair_bar);
-      ok = wait_warp(pair_bar, j & 1, ctx, kSitePair, j);
+      if (lane == 0) mbar_arrive(row_bar);
+      ok = wait_warp(row_bar, j & 1, ctx, kSitePair, j);
       if (!ok) break;
-      mx = fmaxf(mx, xchg[j & 1][hf ^ 1][r]) * kLog2e;  // block maximum, log2 domain
+      mx = fmaxf(fmaxf(xchg[j & 1][0][r], xchg[j & 1][1][r]),
+                 fmaxf(xchg[j & 1][2][r], xchg[j & 1][3][r])) * mul;  // block maximum, log2 domain
+      if (tid == 0) TR(0, j, 5);
       const bool need = mx > m_used + 8.0f;
       const bool any_need = __any_sync(0xffffffffu, need);
       // O may only be touched once P_{j-1} V_{j-1} has completed.
@@ -313,6 +336,7 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
         ok = wait_warp(&pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
         if (!ok) break;
       }
+      if (tid == 0) TR(0, j, 6);
       if (any_need) {
         const float m_new = need ? mx : m_used;
         const float alpha = need ? ex2(m_used - m_new) : 1.0f;
@@ -320,26 +344,24 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
         m_used = m_new;
         if (j > 0) {
           tc_fence_after();
+          uint32_t o[kQD];
+          tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < kHalfD / 32; ++g) {
-            uint32_t o[32];
-            tmem_ld32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
-          }
+          for (int i = 0; i < kQD; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
         }
       }
+      if (tid == 0) TR(0, j, 7);
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float p0 = ex2(fmaf(s[2 * i], kLog2e, neg_m));
-        const float p1 = ex2(fmaf(s[2 * i + 1], kLog2e, neg_m));
-        const float p2 = ex2(fmaf(s[2 * i + 2], kLog2e, neg_m));
-        const float p3 = ex2(fmaf(s[2 * i + 3], kLog2e, neg_m));
+      for (int i = 0; i < 16; i += 2) {
+        const float p0 = ex2(fmaf(s[2 * i], mul, neg_m));
+        const float p1 = ex2(fmaf(s[2 * i + 1], mul, neg_m));
+        const float p2 = ex2(fmaf(s[2 * i + 2], mul, neg_m));
+        const float p3 = ex2(fmaf(s[2 * i + 3], mul, neg_m));
         sum0 += p0;
         sum1 += p1;
         sum2 += p2;
@@ -348,50 +370,50 @@ __global__ void __launch_bounds__(320, 1) fwd_kernel(const __grid_constant__ Fwd
         pk[i + 1] = P2::pack(p2, p3);
       }
       l += (sum0 + sum1) + (sum2 + sum3);
-      // P (16 bit) over the S columns: this half's 64 keys -> 32 packed columns
-      tmem_st32(tmem_addr(tmem, lane_base, kColS + st * 128 + hf * 32), pk);
+      if (tid == 0) TR(0, j, 8);
+      // P (16 bit) over the S columns: this quarter's 32 keys -> 16 packed columns
+      tmem_st16(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 16), pk);
       tmem_st_wait();
+      if (tid == 0) TR(0, j, 9);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
+      if (tid == 0) TR(0, j, 10);
     }
     // ---- epilogue: O / l -> global, log-sum-exp
     if (ok) ok = wait_warp(&pv_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
-    // full row sum = own half + partner half
+    // full row sum = sum of the four quarters
     if (ok) {
-      xchg[nblk & 1][hf][r] = l;
+      xchg[nblk & 1][qt][r] = l;
       __syncwarp();
-      if (lane == 0) mbar_arrive(pair_bar);
-      ok = wait_warp(pair_bar, nblk & 1, ctx, kSitePair, nblk);
+      if (lane == 0) mbar_arrive(row_bar);
+      ok = wait_warp(row_bar, nblk & 1, ctx, kSitePair, nblk);
     }
     if (ok) {
-      l += xchg[nblk & 1][hf ^ 1][r];
+      l = (xchg[nblk & 1][0][r] + xchg[nblk & 1][1][r]) + (xchg[nblk & 1][2][r] + xchg[nblk & 1][3][r]);
       tc_fence_after();
       const int m = m0 + r;
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM +
                 h * p.o_sH;
+      uint32_t o[kQD];
+      tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
+      tmem_ld_wait();
+      if (m < p.M) {
 #pragma unroll
-      for (int g = 0; g < kHalfD / 32; ++g) {
-        uint32_t o[32];
-        tmem_ld32(tmem_addr(tmem, lane_base, kColO + hf * kHalfD + g * 32), o);
-        tmem_ld_wait();
-        if (m < p.M) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int d = hf * kHalfD + g * 32 + c * 8;
-            if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + c * 8, inv);
-          }
+        for (int c = 0; c < kQD / 8; ++c) {
+          const int d = qt * kQD + c * 8;
+          if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + c * 8, inv);
         }
       }
-      if (hf == 0 && m < p.M)
+      if (qt == 0 && m < p.M)
         p.lse[(static_cast<int64_t>(bh)) * p.M + m] = l > 0.f ? m_used + log2f(l) : INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 17) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int DP, typename T, int BIAS>
@@ -407,7 +429,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 320, L::kDynamic, stream>>>(fp);
+  kern<<<grid, 576, L::kDynamic, stream>>>(fp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 
@@ -422,6 +444,13 @@ int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stre
 }
 
 }  // namespace
+
+#ifdef FA_TRACE
+extern "C" int fa_debug_read_trace(long long* out, int n) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   FwdParams fp;
