@@ -12,7 +12,7 @@ What it restates (reference project file `flash_attention.py`, cited as FA:<line
     key n visible to query m iff m >= n                      FA:45
   * float bias added to the scaled scores before the softmax FA:51-53
   * out = softmax(s) . v, log2-domain log-sum-exp saved      FA:55-70, FA:188-194
-  * delta = rowsum(o * do)                                   FA:197-233
+  * delta = rowsum(o * do), o being the saved 16-bit output  FA:197-233, FA:653
   * dv = p^T . do ; dp = do . v^T ; ds = p * (dp - delta)    FA:294-306
   * dbias = ds                                               FA:307-308
   * dk = sm_scale * ds^T . q                                 FA:310, FA:449
@@ -81,7 +81,10 @@ def attention_backward(q, k, v, bias, causal, sm_scale, do):
     vf = v.float().transpose(1, 2)
     qf = q.float().transpose(1, 2)
     kf = k.float().transpose(1, 2)
-    delta = (out.transpose(1, 2) * dof).sum(-1)  # (B, H, M)
+    # The reference saves `o` in q's dtype (FA:653) and its preprocess kernel reads that
+    # tensor (FA:207-219), so delta is formed from the ROUNDED output.
+    o_saved = out.to(q.dtype).float() if q.dtype in (torch.float16, torch.bfloat16) else out
+    delta = (o_saved.transpose(1, 2) * dof).sum(-1)  # (B, H, M)
     dv = torch.matmul(p.transpose(-1, -2), dof)
     dp = torch.matmul(dof, vf.transpose(-1, -2))
     ds = p * (dp - delta.unsqueeze(-1))

@@ -167,3 +167,79 @@ def test_bad_arguments_raise():
         flash_attention_fn(x, x, x)
     with pytest.raises(TypeError):
         flash_attention_fn(q.float(), q.float(), q.float())
+
+
+# ---- against the reference's own outputs (golden vectors made by its Triton kernels)
+from tests import _golden  # noqa: E402
+
+
+@pytest.mark.parametrize("name", _golden.names())
+def test_against_reference_golden_vectors(name, device_ok):
+    from triton_flashattn_b200 import flash_attention_fn, flash_attention_qkvpacked_fn
+
+    g = _golden.load(name)
+    bias = g.get("bias")
+    if bias is not None:
+        bias = bias.cuda()
+    do = g["do"].cuda()
+    tol = 5e-3  # both sides are fp16 results of the same algorithm
+    if g["packed"]:
+        x = g["qkv"].cuda().requires_grad_()
+        out = flash_attention_qkvpacked_fn(x, bias, g["causal"], g["sm_scale"])
+        out.backward(do)
+        assert (out.float().cpu() - g["out"].float()).abs().max().item() <= tol
+        assert (x.grad.float().cpu() - g["dqkv"].float()).abs().max().item() <= tol
+        return
+    q, k, v = (g[n].cuda().requires_grad_() for n in ("q", "k", "v"))
+    trainable = "dbias" in g
+    if trainable:
+        bias = bias.requires_grad_()
+    out = flash_attention_fn(q, k, v, bias, g["causal"], g["sm_scale"])
+    out.backward(do)
+    assert (out.float().cpu() - g["out"].float()).abs().max().item() <= tol
+    for n, t in (("dq", q), ("dk", k), ("dv", v)):
+        assert (t.grad.float().cpu() - g[n].float()).abs().max().item() <= tol, n
+    if trainable:
+        assert (bias.grad.float().cpu() - g["dbias"].float()).abs().max().item() <= tol
+
+
+# ---- the benchmark configurations at their full M, N, D (reduced batch/heads), checked
+# ---- slice by slice against the fp32 oracle with the stated tolerances
+@pytest.mark.parametrize("cfg", ["2", "3", "4", "5"])
+def test_benchmark_config_shapes(cfg, device_ok):
+    from triton_flashattn_b200 import flash_attention_fn, flash_attention_qkvpacked_fn
+
+    spec = {"2": (2, 4, 1024, 64, None, True), "3": (1, 4, 2048, 128, "float", False),
+            "4": (1, 2, 4096, 128, "bool", True), "5": (1, 1, 8192, 128, "float", True)}[cfg]
+    B, H, S, D, bias_kind, causal = spec
+    q, k, v, bias, do = make_inputs(B, S, S, H, D, BF, bias_kind, int(cfg), bias_scale=0.5)
+    if cfg == "4":
+        qkv = torch.stack([q, k, v], dim=2).requires_grad_()
+        out = flash_attention_qkvpacked_fn(qkv, bias, causal, None)
+        out.backward(do)
+        ours = {"out": out.detach(), "dq": qkv.grad[:, :, 0], "dk": qkv.grad[:, :, 1], "dv": qkv.grad[:, :, 2]}
+    else:
+        ours = run_ours(q, k, v, bias, causal, None, do)
+    worst = {}
+    for b in range(B):
+        for h in range(H):
+            sl = lambda t: t[b:b + 1, :, h:h + 1]
+            bb = None if bias is None else bias[b:b + 1, h:h + 1]
+            ref = oracle.attention_backward(sl(q), sl(k), sl(v), bb, causal, None, sl(do))
+            part = {n: sl(t) for n, t in ours.items() if n != "dbias"}
+            if "dbias" in ours:
+                part["dbias"] = ours["dbias"][b:b + 1, h:h + 1]
+            from tests._util import errors
+            for n, (e_abs, e_exc) in errors(part, ref, BF).items():
+                worst[n] = max(worst.get(n, (0, 0)), (e_abs, e_exc))
+    print(f"config {cfg} shape: " + " ".join(f"{n}={e[0]:.2e}" for n, e in worst.items()))
+    for n, (e_abs, e_exc) in worst.items():
+        assert e_exc <= 2e-2, f"{n}: {e_abs:.3e}"
+    if cfg == "4":
+        # the mask pattern is reproduced exactly: masked-out keys get exactly zero probability,
+        # so dk/dv of a key that no query may see are exactly zero -- checked on a tiny extra case
+        m = torch.ones(1, 1, 128, 128, dtype=torch.bool, device="cuda")
+        m[..., 7] = False
+        qq, kk, vv, _, dd = make_inputs(1, 128, 128, 1, 64, BF, None, 1)
+        r = run_ours(qq, kk, vv, m, False, None, dd)
+        assert torch.all(r["dk"][0, 7] == 0) and torch.all(r["dv"][0, 7] == 0)

@@ -1,12 +1,16 @@
 // dK / dV (and dbias) kernel for sm_100a.
 //
 // One CTA owns 128 keys of one (batch, head) and walks the query blocks of 128
-// rows (only those at or below the diagonal when causal).  Roles (576 threads):
+// rows (only those at or below the diagonal when causal).  Roles (640 threads):
 //   warps 0-15 "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
 //              (query rows of the block) and on the 32-key column quarter (w>>2)
 //   warp 16    TMA producer (one lane): K, V once; Q ring (2), dO ring
-//   warp 17    MMA issuer (one lane), tensor-memory owner
-//   warp 18    bulk tensor stores of the dS tile into dbias (one lane)
+//   warp 17    MMA issuer for S and dP (one lane), tensor-memory owner
+//   warp 18    MMA issuer for dV and dK (one lane)
+//   warp 19    bulk tensor stores of the dS tile into dbias (one lane)
+// A barrier operation answers after ~200 cycles on this GPU, so two issuers keep
+// the tensor pipe fed while the other one waits, and every role polls the
+// barriers it will need before it starts a stretch of independent work.
 // Per query block t:
 //   S  = Q_t K^T            (tensor memory, 128 columns)
 //   dP = dO_t V^T           (tensor memory, 128 columns)
@@ -74,7 +78,7 @@ struct DkdvSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ DkdvParams p) {
+__global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ DkdvParams p) {
   using L = DkdvSmem<DP>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;
@@ -111,9 +115,9 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
     mbar_init(&kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 1);
+      mbar_init(&q_empty[i], 2);
       mbar_init(&do_full[i], 1);
-      mbar_init(&do_empty[i], 1);
+      mbar_init(&do_empty[i], 2);
     }
     mbar_init(&s_full, 1);
     mbar_init(&dp_full, 1);
@@ -185,94 +189,106 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       }
     }
   } else if (warp == 17) {
-    // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0 && live) {
+    // ------------------------------------------------------- MMA issuer: S and dP
+    if (lane == 0 && live && T_steps > 0) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
-      constexpr uint32_t idesc_g = make_idesc(bf, true, true, 128, DP);
       const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
-      const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDs);
-      bool ok = true;
-      // slice-0 descriptors: K-major views (S, dP) and MN-major views (dV, dK)
       const uint64_t k_km = make_sdesc(k_addr, 0, 1024), v_km = make_sdesc(v_addr, 0, 1024);
       const uint64_t q_km_0 = make_sdesc(q_addr, 0, 1024), q_km_1 = make_sdesc(q_addr + L::kTile, 0, 1024);
-      const uint64_t q_mn_0 = make_sdesc(q_addr, kBlk, 1024), q_mn_1 = make_sdesc(q_addr + L::kTile, kBlk, 1024);
-      const uint64_t do_km_0 = make_sdesc(do_addr, 0, 1024), do_km_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, 0, 1024);
-      const uint64_t do_mn_0 = make_sdesc(do_addr, kBlk, 1024), do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
-      const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
+      const uint64_t do_km_0 = make_sdesc(do_addr, 0, 1024),
+                     do_km_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, 0, 1024);
       auto issue_s = [&](int t) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColS, ((t & 1) ? q_km_1 : q_km_0), k_km, kBlk, kBlk, idesc_s, false);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColS, (t & 1) ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
+                                          idesc_s, false);
         mma_commit(&s_full);
+        mma_commit(&q_empty[t & 1]);
       };
       auto issue_dp = [&](int t) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ((t % kDoStages) ? do_km_1 : do_km_0), v_km, kBlk, kBlk,
-                                          idesc_s, false);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, (t % kDoStages) ? do_km_1 : do_km_0, v_km,
+                                          kBlk, kBlk, idesc_s, false);
         mma_commit(&dp_full);
+        mma_commit(&do_empty[t % kDoStages]);
       };
-      if (ok && T_steps > 0) {
-        ok = mbar_wait(&kv_full, 0, ctx, kSiteKV, 0);
-        if (ok) ok = mbar_wait(&q_full[0], 0, ctx, kSiteQFull, 0);
-        if (ok) {
-          tc_fence_after();
-          issue_s(0);
-          ok = mbar_wait(&do_full[0], 0, ctx, kSiteDoFull, 0);
-        }
-        if (ok) {
-          tc_fence_after();
-          issue_dp(0);
-        }
+      bool ok = mbar_wait(&kv_full, 0, ctx, kSiteKV, 0);
+      if (ok) ok = mbar_wait(&q_full[0], 0, ctx, kSiteQFull, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        ok = mbar_wait(&do_full[0], 0, ctx, kSiteDoFull, 0);
       }
-      for (int t = 0; t < T_steps && ok; ++t) {
-        const int qs = t & 1;
-        const int ds = t % kDoStages;
-        // S of the next block as soon as the row threads hold S_t in registers
-        TR(1, t, 0);
-        if (t + 1 < T_steps) {
-          ok = mbar_wait(&s_free, t & 1, ctx, kSiteSFree, t);
-          TR(1, t, 1);
-          if (ok) ok = mbar_wait(&q_full[(t + 1) & 1], ((t + 1) >> 1) & 1, ctx, kSiteQFull, t + 1);
-          if (!ok) break;
-          TR(1, t, 2);
-          tc_fence_after();
-          issue_s(t + 1);
-          TR(1, t, 3);
-        }
-        // dV += P^T dO
-        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
+      }
+      for (int t = 0; t + 1 < T_steps && ok; ++t) {
+        const int ds1 = (t + 1) % kDoStages;
+        const uint32_t q_par = ((t + 1) >> 1) & 1, do_par = ((t + 1) / kDoStages) & 1;
+        // S_{t+1}: its columns are free once the row threads hold S_t in registers
+        const uint32_t pq = mbar_poll(&q_full[(t + 1) & 1], q_par);
+        ok = mbar_wait(&s_free, t & 1, ctx, kSiteSFree, t);
+        if (ok) ok = wait_polled(pq, &q_full[(t + 1) & 1], q_par, ctx, kSiteQFull, t + 1);
         if (!ok) break;
+        TR(1, t, 1);
+        tc_fence_after();
+        const uint32_t pdo = mbar_poll(&do_full[ds1], do_par);
+        issue_s(t + 1);
+        TR(1, t, 2);
+        // dP_{t+1}: same for the dP columns; dO_{t+1} replaces dO_t after dV_t when single-staged
+        ok = mbar_wait(&dp_free, t & 1, ctx, kSiteDpFree, t);
+        if (ok) ok = wait_polled(pdo, &do_full[ds1], do_par, ctx, kSiteDoFull, t + 1);
+        if (!ok) break;
+        TR(1, t, 3);
+        tc_fence_after();
+        issue_dp(t + 1);
         TR(1, t, 4);
-        tc_fence_after();
-        issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ((ds) ? do_mn_1 : do_mn_0), kBlk, kBlk, idesc_g, t > 0);
-        mma_commit(&do_empty[ds]);
-        mma_commit(&dv_done);
-        TR(1, t, 5);
-        // dK += dS^T Q
-        TR(1, t, 6);
-        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
-        if (!ok) break;
-        TR(1, t, 7);
-        tc_fence_after();
-        issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, ((qs) ? q_mn_1 : q_mn_0), kBlk, kBlk, idesc_g, t > 0);
-        mma_commit(&q_empty[qs]);
-        mma_commit(&dk_done);
-        TR(1, t, 8);
-        // dP of the next block (its columns were handed back before dS_t was written)
-        if (t + 1 < T_steps) {
-          const int ds1 = (t + 1) % kDoStages;
-          ok = mbar_wait(&dp_free, t & 1, ctx, kSiteDpFree, t);
-          TR(1, t, 9);
-          if (ok) ok = mbar_wait(&do_full[ds1], ((t + 1) / kDoStages) & 1, ctx, kSiteDoFull, t + 1);
-          if (!ok) break;
-          TR(1, t, 10);
-          tc_fence_after();
-          issue_dp(t + 1);
-          TR(1, t, 11);
-        }
       }
     }
     __syncwarp();
   } else if (warp == 18) {
+    // ------------------------------------------------------ MMA issuer: dV and dK
+    if (lane == 0 && live) {
+      constexpr bool bf = P2::kIsBf16;
+      constexpr uint32_t idesc_g = make_idesc(bf, true, true, 128, DP);
+      const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
+      const uint32_t p_addr = smem_u32(smem + L::kP), ds_addr = smem_u32(smem + L::kDs);
+      const uint64_t q_mn_0 = make_sdesc(q_addr, kBlk, 1024), q_mn_1 = make_sdesc(q_addr + L::kTile, kBlk, 1024);
+      const uint64_t do_mn_0 = make_sdesc(do_addr, kBlk, 1024),
+                     do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
+      const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
+      bool ok = true;
+      for (int t = 0; t < T_steps && ok; ++t) {
+        const int qs = t & 1;
+        const int ds = t % kDoStages;
+        // dV += P^T dO  (dO_t must have landed: P_t only depends on S_t)
+        const uint32_t pdo = mbar_poll(&do_full[ds], (t / kDoStages) & 1);
+        const uint32_t pq = mbar_poll(&q_full[qs], (t >> 1) & 1);
+        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
+        if (ok) ok = wait_polled(pdo, &do_full[ds], (t / kDoStages) & 1, ctx, kSiteDoFull, t);
+        if (!ok) break;
+        TR(2, t, 1);
+        tc_fence_after();
+        issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
+                                     t > 0);
+        mma_commit(&do_empty[ds]);
+        mma_commit(&dv_done);
+        TR(2, t, 2);
+        // dK += dS^T Q
+        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
+        if (ok) ok = wait_polled(pq, &q_full[qs], (t >> 1) & 1, ctx, kSiteQFull, t);
+        if (!ok) break;
+        TR(2, t, 3);
+        tc_fence_after();
+        issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
+                                     t > 0);
+        mma_commit(&q_empty[qs]);
+        mma_commit(&dk_done);
+        TR(2, t, 4);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 19) {
     // ------------------------------------------------------------- dbias stores
     // phase 0 of st_done: zero tiles above the diagonal are out (or nothing to do);
     // phase t+1: the store of dS_t has finished reading sDS.
@@ -335,20 +351,24 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       if (BIAS != 0)
         load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N,
                             p.bias_vec32 != 0);
-      lse_next = row_ok ? __ldg(p.lse + (int64_t)bh * p.M + m) : INFINITY;
-      delta_next = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
+      // clamped address: the value of a row beyond M is replaced when it is used
+      const int mc = row_ok ? m : p.M - 1;
+      lse_next = __ldg(p.lse + (int64_t)bh * p.M + mc);
+      delta_next = __ldg(p.delta + (int64_t)bh * p.M + mc);
     };
     if (ok && T_steps > 0) prefetch(0);
 
     for (int t = 0; t < T_steps && ok; ++t) {
       const int m0 = (i_start + t) * 128;
       BiasRegs<BIAS> bcur = bnext;
-      const float lse_cur = lse_next, delta_r = delta_next;
+      const bool row_in = m0 + r < p.M;
+      const float lse_raw = lse_next, delta_raw = delta_next;
       if (t + 1 < T_steps) prefetch(t + 1);
+      const uint32_t ps = mbar_poll(&s_full, t & 1);
 
       // ---- P
       if (tid == 0) TR(0, t, 0);
-      ok = wait_warp(&s_full, t & 1, ctx, kSiteSFull, t);
+      ok = wait_warp_polled(ps, &s_full, t & 1, ctx, kSiteSFull, t);
       if (!ok) break;
       if (tid == 0) TR(0, t, 1);
       tc_fence_after();
@@ -359,8 +379,12 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free);
+      // barriers needed after the exponentials: ask now, the answers arrive meanwhile
+      const uint32_t pdv = t >= 1 ? mbar_poll(&dv_done, (t - 1) & 1) : 1u;
+      const uint32_t pdp = mbar_poll(&dp_full, t & 1);
       // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
-      const float neg_lse = -lse_cur;
+      const float neg_lse = row_in ? -lse_raw : -INFINITY;
+      const float delta_r = row_in ? delta_raw : 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         if (BIAS == 1) {
@@ -382,7 +406,7 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       }
       if (tid == 0) TR(0, t, 2);
       if (t >= 1) {
-        ok = wait_warp(&dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
+        ok = wait_warp_polled(pdv, &dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
         if (!ok) break;
       }
       if (tid == 0) TR(0, t, 3);
@@ -401,7 +425,9 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       if (tid == 0) TR(0, t, 4);
 
       // ---- dS
-      ok = wait_warp(&dp_full, t & 1, ctx, kSiteDpFull, t);
+      const uint32_t pdk = t >= 1 ? mbar_poll(&dk_done, (t - 1) & 1) : 1u;
+      const uint32_t pst = p.write_dbias ? mbar_poll(&st_done, t & 1) : 1u;
+      ok = wait_warp_polled(pdp, &dp_full, t & 1, ctx, kSiteDpFull, t);
       if (!ok) break;
       if (tid == 0) TR(0, t, 5);
       tc_fence_after();
@@ -422,12 +448,12 @@ __global__ void __launch_bounds__(608, 1) dkdv_kernel(const __grid_constant__ Dk
       }
       if (tid == 0) TR(0, t, 6);
       if (t >= 1) {
-        ok = wait_warp(&dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
+        ok = wait_warp_polled(pdk, &dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
         if (!ok) break;
       }
       if (tid == 0) TR(0, t, 7);
       if (p.write_dbias) {
-        ok = wait_warp(&st_done, t & 1, ctx, kSiteStDone, t);
+        ok = wait_warp_polled(pst, &st_done, t & 1, ctx, kSiteStDone, t);
         if (!ok) break;
       }
       if (tid == 0) TR(0, t, 8);
@@ -496,7 +522,7 @@ int launch_inst(const DkdvParams& kp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 608, L::kDynamic, stream>>>(kp);
+  kern<<<grid, 640, L::kDynamic, stream>>>(kp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 

@@ -77,6 +77,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking look at a phase.  A barrier operation takes ~200 cycles to answer on
+// B200, so the result is requested early (before a stretch of independent work) and
+// consumed later with wait_polled / wait_warp_polled.
+__device__ __forceinline__ uint32_t mbar_poll(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -494,6 +511,19 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, const 
                                           int site, int iter) {
   const bool ok = mbar_wait(bar, parity, ctx, site, iter);
   return __all_sync(0xffffffffu, ok);
+}
+
+// Finish a wait whose phase was polled earlier: no further barrier traffic when the
+// poll had already seen the phase complete.
+__device__ __forceinline__ bool wait_polled(uint32_t polled, uint64_t* bar, uint32_t parity,
+                                            const WaitCtx& ctx, int site, int iter) {
+  if (polled) return true;
+  return mbar_wait(bar, parity, ctx, site, iter);
+}
+__device__ __forceinline__ bool wait_warp_polled(uint32_t polled, uint64_t* bar, uint32_t parity,
+                                                 const WaitCtx& ctx, int site, int iter) {
+  if (__all_sync(0xffffffffu, polled != 0)) return true;
+  return wait_warp(bar, parity, ctx, site, iter);
 }
 
 // 32 bias values of one row quarter, as raw 16-bit pairs (BIAS == 1) or bytes (BIAS == 2).

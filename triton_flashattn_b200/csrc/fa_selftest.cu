@@ -135,6 +135,108 @@ __global__ void __launch_bounds__(128, 1) selftest_kernel(const __grid_constant_
       }
     }
   }
+#ifdef FA_TRACE
+  if (p.mode == 0 && tid == 0) {
+    // latency micro-measurements (cycles), written after the result matrix
+    long long t0 = clock64();
+    long long t1 = clock64();
+    p.c[128 * 128 + 0] = float(t1 - t0);  // clock64 back to back
+    t0 = clock64();
+    for (int i = 0; i < 16; ++i) mbar_wait(&bar_load, 0, ctx, 9);  // already complete
+    t1 = clock64();
+    p.c[128 * 128 + 1] = float(t1 - t0) / 16.f;
+    __shared__ uint64_t bar_x;
+    mbar_init(&bar_x, 1);
+    mbar_fence_init();
+    t0 = clock64();
+    mbar_arrive(&bar_x);
+    mbar_wait(&bar_x, 0, ctx, 9);
+    t1 = clock64();
+    p.c[128 * 128 + 2] = float(t1 - t0);  // arrive + wait round trip
+    t0 = clock64();
+    mma_commit(&bar_x);  // nothing outstanding: commit -> arrive latency
+    mbar_wait(&bar_x, 1, ctx, 9);
+    t1 = clock64();
+    p.c[128 * 128 + 3] = float(t1 - t0);
+    // one 128x128x16 MMA: issue -> commit -> wait
+    const uint32_t idesc = make_idesc(bf, false, false, 128, 128);
+    t0 = clock64();
+    mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, 0), sdesc_kmajor(b_addr, kTile / 2, 0), idesc, false);
+    long long t_issue = clock64();
+    mma_commit(&bar_x);
+    mbar_wait(&bar_x, 0, ctx, 9);
+    t1 = clock64();
+    p.c[128 * 128 + 4] = float(t_issue - t0);
+    p.c[128 * 128 + 5] = float(t1 - t0);
+    // eight MMAs (one 128^3 tile product)
+    t0 = clock64();
+    for (int ks = 0; ks < 8; ++ks)
+      mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, ks), sdesc_kmajor(b_addr, kTile / 2, ks), idesc, ks > 0);
+    t_issue = clock64();
+    mma_commit(&bar_x);
+    mbar_wait(&bar_x, 1, ctx, 9);
+    t1 = clock64();
+    p.c[128 * 128 + 6] = float(t_issue - t0);
+    p.c[128 * 128 + 7] = float(t1 - t0);
+    // 4 x 8 MMAs back to back
+    t0 = clock64();
+    for (int rep = 0; rep < 4; ++rep)
+      for (int ks = 0; ks < 8; ++ks)
+        mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, ks), sdesc_kmajor(b_addr, kTile / 2, ks), idesc, ks > 0);
+    t_issue = clock64();
+    mma_commit(&bar_x);
+    mbar_wait(&bar_x, 0, ctx, 9);
+    t1 = clock64();
+    p.c[128 * 128 + 8] = float(t_issue - t0);
+    p.c[128 * 128 + 9] = float(t1 - t0);
+    // raw barrier polls on a completed phase (bar_load, parity 0), one by one
+    for (int i = 0; i < 4; ++i) {
+      t0 = clock64();
+      const bool a = mbar_try_wait(&bar_load, 0);
+      t1 = clock64();
+      p.c[128 * 128 + 16 + i] = float(t1 - t0) + (a ? 0.f : 1000000.f);
+    }
+    for (int i = 0; i < 4; ++i) {
+      uint32_t okv;
+      t0 = clock64();
+      asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.relaxed.cta.shared::cta.b64 P, [%1], %2;\nselp.b32 %0, 1, 0, P;\n}"
+                   : "=r"(okv) : "r"(smem_u32(&bar_load)), "r"(0) : "memory");
+      t1 = clock64();
+      p.c[128 * 128 + 20 + i] = float(t1 - t0) + (okv ? 0.f : 1000000.f);
+    }
+    for (int i = 0; i < 4; ++i) {
+      uint32_t okv;
+      t0 = clock64();
+      asm volatile("{\n.reg .pred P;\nmbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.b32 %0, 1, 0, P;\n}"
+                   : "=r"(okv) : "r"(smem_u32(&bar_load)), "r"(0) : "memory");
+      t1 = clock64();
+      p.c[128 * 128 + 24 + i] = float(t1 - t0) + (okv ? 0.f : 1000000.f);
+    }
+    for (int i = 0; i < 4; ++i) {
+      t0 = clock64();
+      const bool a = mbar_wait(&bar_load, 0, ctx, 9);
+      t1 = clock64();
+      p.c[128 * 128 + 28 + i] = float(t1 - t0) + (a ? 0.f : 1000000.f);
+    }
+    {
+      volatile uint32_t* sp = reinterpret_cast<volatile uint32_t*>(sC);
+      t0 = clock64();
+      uint32_t v = sp[0];
+      t1 = clock64();
+      p.c[128 * 128 + 32] = float(t1 - t0) + (v == 0x12345 ? 1.f : 0.f);
+    }
+    t0 = clock64();
+    fence_proxy_async_smem();
+    t1 = clock64();
+    p.c[128 * 128 + 11] = float(t1 - t0);
+    t0 = clock64();
+    tc_fence_before();
+    tc_fence_after();
+    t1 = clock64();
+    p.c[128 * 128 + 12] = float(t1 - t0);
+  }
+  __syncwarp();
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
