@@ -1,12 +1,15 @@
 // Forward attention kernel for sm_100a.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
-// 128 keys.  Roles (576 threads):
+// 128 keys.  Roles (608 threads):
 //   warps 0-15 softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
 //              lanes) and the 32-key quarter (w>>2) of every block; the four
 //              quarters of a row exchange partial maxima through shared memory
 //   warp 16    TMA producer (one elected lane): Q once, K / V rings, bias ring
-//   warp 17    MMA issuer (one lane) and tensor-memory owner
+//   warp 17    MMA issuer for S = Q K^T (one lane), tensor-memory owner
+//   warp 18    MMA issuer for O += P V (one lane)
+// A barrier operation answers after ~200 cycles on this GPU; two issuers keep the
+// tensor pipe fed while one of them waits, and barriers are polled ahead of use.
 // Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
 // in tensor memory, double buffered) -> softmax threads read S_j, add the bias
 // tile (streamed by TMA into a shared-memory ring), apply masks, run the online
@@ -64,7 +67,7 @@ struct FwdSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(608, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
@@ -174,50 +177,50 @@ __global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ Fwd
       }
     }
   } else if (warp == 17) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ------------------------------------------------------- MMA issuer: S = Q K^T
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 128);
-      constexpr uint32_t idesc_pv = make_idesc(bf, false, true, 128, DP);
       const uint32_t q_addr = smem_u32(smem + L::kQ);
       const uint32_t k_addr = smem_u32(smem + L::kK);
-      const uint32_t v_addr = smem_u32(smem + L::kV);
       const uint64_t q_desc = make_sdesc(q_addr, 0, 1024);
       const uint64_t k_desc_0 = make_sdesc(k_addr, 0, 1024), k_desc_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
-      const uint64_t v_desc_0 = make_sdesc(v_addr, kBlk, 1024), v_desc_1 = make_sdesc(v_addr + L::kTile, kBlk, 1024);
-      auto issue_qk = [&](int j) {
-        const int st = j & 1;
-        issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc, ((st) ? k_desc_1 : k_desc_0), kBlk, kBlk,
-                                           idesc_qk, false);
-        mma_commit(&s_full[st]);
-        mma_commit(&k_empty[st]);
-      };
       bool ok = mbar_wait(&q_full, 0, ctx, kSiteQ, 0);
-      if (ok) ok = mbar_wait(&k_full[0], 0, ctx, kSiteKFull, 0);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0);
-      }
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j & 1;
-        TR(1, j, 0);
-        if (j + 1 < nblk) {
-          ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, ctx, kSiteKFull, j + 1);
-          if (!ok) break;
-          TR(1, j, 1);
-          tc_fence_after();
-          issue_qk(j + 1);
-          TR(1, j, 2);
-        }
-        ok = mbar_wait(&v_full[st], (j >> 1) & 1, ctx, kSiteVFull, j);
+        const uint32_t pk = mbar_poll(&k_full[st], (j >> 1) & 1);
+        // S_j overwrites the columns that held P_{j-2}: P_{j-2} V_{j-2} must be through
+        if (j >= 2) ok = mbar_wait(&pv_done, (j - 2) & 1, ctx, kSitePvDone, j);
+        if (ok) ok = wait_polled(pk, &k_full[st], (j >> 1) & 1, ctx, kSiteKFull, j);
         if (!ok) break;
-        TR(1, j, 3);
+        TR(1, j, 1);
+        tc_fence_after();
+        issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc, st ? k_desc_1 : k_desc_0,
+                                           kBlk, kBlk, idesc_qk, false);
+        mma_commit(&s_full[st]);
+        mma_commit(&k_empty[st]);
+        TR(1, j, 2);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 18) {
+    // ------------------------------------------------------- MMA issuer: O += P V
+    if (lane == 0 && live) {
+      constexpr bool bf = P2::kIsBf16;
+      constexpr uint32_t idesc_pv = make_idesc(bf, false, true, 128, DP);
+      const uint32_t v_addr = smem_u32(smem + L::kV);
+      const uint64_t v_desc_0 = make_sdesc(v_addr, kBlk, 1024), v_desc_1 = make_sdesc(v_addr + L::kTile, kBlk, 1024);
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t pv = mbar_poll(&v_full[st], (j >> 1) & 1);
         ok = mbar_wait(&p_full, j & 1, ctx, kSitePFull, j);
+        if (ok) ok = wait_polled(pv, &v_full[st], (j >> 1) & 1, ctx, kSiteVFull, j);
         if (!ok) break;
         TR(1, j, 4);
         tc_fence_after();
-        issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, ((st) ? v_desc_1 : v_desc_0), kBlk, idesc_pv,
-                               j > 0);
+        issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, st ? v_desc_1 : v_desc_0, kBlk,
+                               idesc_pv, j > 0);
         mma_commit(&v_empty[st]);
         mma_commit(&pv_done);
         TR(1, j, 5);
@@ -237,11 +240,14 @@ __global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ Fwd
     const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
     const float scale_log2 = p.sm_scale * kLog2e;
     uint32_t unit = BIAS == 1 ? (qt >> 1) : 0;  // 16-bit bias: units hf, hf+2, ...; mask: one per block
+    uint32_t ps_next = 0;  // early look at the barrier of the next block's scores
     for (int j = 0; j < nblk && ok; ++j) {
       const int st = j & 1;
       const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
       if (tid == 0) TR(0, j, 0);
-      ok = wait_warp(&s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
+      // barriers of this step that are probably complete already: ask first, use later
+      const uint32_t pbias = BIAS != 0 ? mbar_poll(&bias_full[unit % NB], (unit / NB) & 1) : 1u;
+      ok = wait_warp_polled(ps_next, &s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
       if (tid == 0) TR(0, j, 1);
       tc_fence_after();
@@ -262,7 +268,7 @@ __global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ Fwd
         }
       } else {
         const int bs = unit % NB;
-        ok = wait_warp(&bias_full[bs], (unit / NB) & 1, ctx, kSiteBiasFull, j);
+        ok = wait_warp_polled(pbias, &bias_full[bs], (unit / NB) & 1, ctx, kSiteBiasFull, j);
         if (!ok) break;
         const uint8_t* tile = smem + L::kBias + bs * kBlk;
         if (BIAS == 1) {
@@ -322,6 +328,7 @@ __global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ Fwd
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       if (tid == 0) TR(0, j, 4);
       xchg[j & 1][qt][r] = mx;
+      const uint32_t ppv = j > 0 ? mbar_poll(&pv_done, (j - 1) & 1) : 1u;
       __syncwarp();
       if (lane == 0) mbar_arrive(row_bar);
       ok = wait_warp(row_bar, j & 1, ctx, kSitePair, j);
@@ -333,7 +340,7 @@ __global__ void __launch_bounds__(576, 1) fwd_kernel(const __grid_constant__ Fwd
       const bool any_need = __any_sync(0xffffffffu, need);
       // O may only be touched once P_{j-1} V_{j-1} has completed.
       if (j > 0) {
-        ok = wait_warp(&pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
+        ok = wait_warp_polled(ppv, &pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
         if (!ok) break;
       }
       if (tid == 0) TR(0, j, 6);
@@ -429,7 +436,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 576, L::kDynamic, stream>>>(fp);
+  kern<<<grid, 608, L::kDynamic, stream>>>(fp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 

@@ -136,6 +136,85 @@ __global__ void __launch_bounds__(128, 1) selftest_kernel(const __grid_constant_
     }
   }
 #ifdef FA_TRACE
+  {
+    // wake-up latency: thread 32 waits, thread 0 arrives after a delay
+    __shared__ uint64_t bar_y, bar_z;
+    __shared__ long long t_arrive[4];
+    if (tid == 0) { mbar_init(&bar_y, 1); mbar_init(&bar_z, 16); mbar_fence_init(); }
+    __syncthreads();
+    if (p.mode == 0) {
+      for (int rep = 0; rep < 2; ++rep) {
+        if (tid == 0) {
+          long long t = clock64();
+          while (clock64() - t < 3000) {}
+          t_arrive[rep] = clock64();
+          mbar_arrive(&bar_y);
+        } else if (tid == 32) {
+          mbar_wait(&bar_y, rep, ctx, 9);
+          long long t = clock64();
+          p.c[128 * 128 + 40 + rep] = float(t - *(volatile long long*)&t_arrive[rep]);
+        }
+        __syncthreads();
+      }
+      // 16 arrivals (lane 0 of 4 warps x 4 times) then one waiter: how long from first to wake
+      if ((tid & 31) == 0) {
+        long long t = clock64();
+        while (clock64() - t < 3000) {}
+        if (tid == 0) t_arrive[2] = clock64();
+        if (tid != 32) { for (int i = 0; i < (tid == 0 ? 6 : 5); ++i) mbar_arrive(&bar_z); }
+        else {
+          mbar_wait(&bar_z, 0, ctx, 9);
+          long long t2 = clock64();
+          p.c[128 * 128 + 42] = float(t2 - *(volatile long long*)&t_arrive[2]);
+        }
+      }
+      __syncthreads();
+      // named barrier: warp 0 arrives after a delay, warp 1 syncs
+      if (warp == 0) {
+        long long t = clock64();
+        while (clock64() - t < 3000) {}
+        if (tid == 0) t_arrive[3] = clock64();
+        __syncwarp();
+        asm volatile("bar.arrive 1, 64;" ::: "memory");
+      } else if (warp == 1) {
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+        long long t2 = clock64();
+        if (tid == 32) p.c[128 * 128 + 43] = float(t2 - *(volatile long long*)&t_arrive[3]);
+      }
+      __syncthreads();
+      // shared-memory flag: thread 0 sets, thread 32 spins on a volatile load
+      __shared__ volatile uint32_t flag;
+      __shared__ uint32_t counter;
+      if (tid == 0) { flag = 0; counter = 0; }
+      __syncthreads();
+      if (tid == 0) {
+        long long t = clock64();
+        while (clock64() - t < 3000) {}
+        t_arrive[0] = clock64();
+        __threadfence_block();
+        flag = 1;
+      } else if (tid == 32) {
+        while (flag == 0) {}
+        __threadfence_block();
+        long long t2 = clock64();
+        p.c[128 * 128 + 44] = float(t2 - *(volatile long long*)&t_arrive[0]);
+      }
+      __syncthreads();
+      // 16 atomic increments (lane 0 of 4 warps, 4 each) then a spinning reader
+      if ((tid & 31) == 0) {
+        long long t = clock64();
+        while (clock64() - t < 3000) {}
+        if (tid == 0) t_arrive[1] = clock64();
+        if (tid != 32) { for (int i = 0; i < (tid == 0 ? 6 : 5); ++i) atomicAdd(&counter, 1u); }
+        else {
+          while (*(volatile uint32_t*)&counter < 16u) {}
+          long long t2 = clock64();
+          p.c[128 * 128 + 45] = float(t2 - *(volatile long long*)&t_arrive[1]);
+        }
+      }
+      __syncthreads();
+    }
+  }
   if (p.mode == 0 && tid == 0) {
     // latency micro-measurements (cycles), written after the result matrix
     long long t0 = clock64();
