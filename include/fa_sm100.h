@@ -114,6 +114,22 @@ int fa_fwd(const fa_params* p, void* stream);
  */
 int fa_bwd(const fa_params* p, void* stream);
 
+/*
+ * Backward for callers that cannot allocate device memory (a plugin living inside a
+ * host runtime with a frozen memory plan, a real-time loop, a foreign-language
+ * binding without an allocator).  Same as fa_bwd, except that `p->delta` is ignored:
+ * the row-sum scratch lives in a fixed 8 MiB device array inside the library.
+ *   - limit: B * H * M <= 2,097,152, else FA_ERR_TOO_LARGE;
+ *   - the first call on a device resolves the array's device address; make it before
+ *     any stream capture starts;
+ *   - all calls on a device share the array: calls that overlap on the GPU race,
+ *     nothing in it has to be cleared between calls;
+ *   - no cudaMalloc / cudaFree or other allocating call is made.
+ * This entry point has no counterpart in the reference (its launcher allocates
+ * `delta` with torch.empty_like on every call).
+ */
+int fa_bwd_static_scratch(const fa_params* p, void* stream);
+
 /* The three backward stages on their own (per-kernel timing and tests). */
 int fa_bwd_pre(const fa_params* p, void* stream);  /* _attn_bwd_preprocess FA:197-233 */
 int fa_bwd_dkdv(const fa_params* p, void* stream); /* _attn_bwd_dkdv       FA:330-454 */

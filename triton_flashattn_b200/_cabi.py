@@ -65,6 +65,7 @@ EXPORTED_SYMBOLS = (
     "fa_status_string",
     "fa_fwd",
     "fa_bwd",
+    "fa_bwd_static_scratch",
     "fa_bwd_pre",
     "fa_bwd_dkdv",
     "fa_bwd_dq",
@@ -96,7 +97,7 @@ def load() -> ctypes.CDLL:
     lib.fa_version.restype = ctypes.c_int
     lib.fa_status_string.restype = ctypes.c_char_p
     lib.fa_status_string.argtypes = [ctypes.c_int]
-    for name in ("fa_fwd", "fa_bwd", "fa_bwd_pre", "fa_bwd_dkdv", "fa_bwd_dq"):
+    for name in ("fa_fwd", "fa_bwd", "fa_bwd_static_scratch", "fa_bwd_pre", "fa_bwd_dkdv", "fa_bwd_dq"):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [P, ctypes.c_void_p]
