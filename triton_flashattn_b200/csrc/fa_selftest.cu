@@ -135,187 +135,6 @@ __global__ void __launch_bounds__(128, 1) selftest_kernel(const __grid_constant_
       }
     }
   }
-#ifdef FA_TRACE
-  {
-    // wake-up latency: thread 32 waits, thread 0 arrives after a delay
-    __shared__ uint64_t bar_y, bar_z;
-    __shared__ long long t_arrive[4];
-    if (tid == 0) { mbar_init(&bar_y, 1); mbar_init(&bar_z, 16); mbar_fence_init(); }
-    __syncthreads();
-    if (p.mode == 0) {
-      for (int rep = 0; rep < 2; ++rep) {
-        if (tid == 0) {
-          long long t = clock64();
-          while (clock64() - t < 3000) {}
-          t_arrive[rep] = clock64();
-          mbar_arrive(&bar_y);
-        } else if (tid == 32) {
-          mbar_wait(&bar_y, rep, ctx, 9);
-          long long t = clock64();
-          p.c[128 * 128 + 40 + rep] = float(t - *(volatile long long*)&t_arrive[rep]);
-        }
-        __syncthreads();
-      }
-      // 16 arrivals (lane 0 of 4 warps x 4 times) then one waiter: how long from first to wake
-      if ((tid & 31) == 0) {
-        long long t = clock64();
-        while (clock64() - t < 3000) {}
-        if (tid == 0) t_arrive[2] = clock64();
-        if (tid != 32) { for (int i = 0; i < (tid == 0 ? 6 : 5); ++i) mbar_arrive(&bar_z); }
-        else {
-          mbar_wait(&bar_z, 0, ctx, 9);
-          long long t2 = clock64();
-          p.c[128 * 128 + 42] = float(t2 - *(volatile long long*)&t_arrive[2]);
-        }
-      }
-      __syncthreads();
-      // named barrier: warp 0 arrives after a delay, warp 1 syncs
-      if (warp == 0) {
-        long long t = clock64();
-        while (clock64() - t < 3000) {}
-        if (tid == 0) t_arrive[3] = clock64();
-        __syncwarp();
-        asm volatile("bar.arrive 1, 64;" ::: "memory");
-      } else if (warp == 1) {
-        asm volatile("bar.sync 1, 64;" ::: "memory");
-        long long t2 = clock64();
-        if (tid == 32) p.c[128 * 128 + 43] = float(t2 - *(volatile long long*)&t_arrive[3]);
-      }
-      __syncthreads();
-      // shared-memory flag: thread 0 sets, thread 32 spins on a volatile load
-      __shared__ volatile uint32_t flag;
-      __shared__ uint32_t counter;
-      if (tid == 0) { flag = 0; counter = 0; }
-      __syncthreads();
-      if (tid == 0) {
-        long long t = clock64();
-        while (clock64() - t < 3000) {}
-        t_arrive[0] = clock64();
-        __threadfence_block();
-        flag = 1;
-      } else if (tid == 32) {
-        while (flag == 0) {}
-        __threadfence_block();
-        long long t2 = clock64();
-        p.c[128 * 128 + 44] = float(t2 - *(volatile long long*)&t_arrive[0]);
-      }
-      __syncthreads();
-      // 16 atomic increments (lane 0 of 4 warps, 4 each) then a spinning reader
-      if ((tid & 31) == 0) {
-        long long t = clock64();
-        while (clock64() - t < 3000) {}
-        if (tid == 0) t_arrive[1] = clock64();
-        if (tid != 32) { for (int i = 0; i < (tid == 0 ? 6 : 5); ++i) atomicAdd(&counter, 1u); }
-        else {
-          while (*(volatile uint32_t*)&counter < 16u) {}
-          long long t2 = clock64();
-          p.c[128 * 128 + 45] = float(t2 - *(volatile long long*)&t_arrive[1]);
-        }
-      }
-      __syncthreads();
-    }
-  }
-  if (p.mode == 0 && tid == 0) {
-    // latency micro-measurements (cycles), written after the result matrix
-    long long t0 = clock64();
-    long long t1 = clock64();
-    p.c[128 * 128 + 0] = float(t1 - t0);  // clock64 back to back
-    t0 = clock64();
-    for (int i = 0; i < 16; ++i) mbar_wait(&bar_load, 0, ctx, 9);  // already complete
-    t1 = clock64();
-    p.c[128 * 128 + 1] = float(t1 - t0) / 16.f;
-    __shared__ uint64_t bar_x;
-    mbar_init(&bar_x, 1);
-    mbar_fence_init();
-    t0 = clock64();
-    mbar_arrive(&bar_x);
-    mbar_wait(&bar_x, 0, ctx, 9);
-    t1 = clock64();
-    p.c[128 * 128 + 2] = float(t1 - t0);  // arrive + wait round trip
-    t0 = clock64();
-    mma_commit(&bar_x);  // nothing outstanding: commit -> arrive latency
-    mbar_wait(&bar_x, 1, ctx, 9);
-    t1 = clock64();
-    p.c[128 * 128 + 3] = float(t1 - t0);
-    // one 128x128x16 MMA: issue -> commit -> wait
-    const uint32_t idesc = make_idesc(bf, false, false, 128, 128);
-    t0 = clock64();
-    mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, 0), sdesc_kmajor(b_addr, kTile / 2, 0), idesc, false);
-    long long t_issue = clock64();
-    mma_commit(&bar_x);
-    mbar_wait(&bar_x, 0, ctx, 9);
-    t1 = clock64();
-    p.c[128 * 128 + 4] = float(t_issue - t0);
-    p.c[128 * 128 + 5] = float(t1 - t0);
-    // eight MMAs (one 128^3 tile product)
-    t0 = clock64();
-    for (int ks = 0; ks < 8; ++ks)
-      mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, ks), sdesc_kmajor(b_addr, kTile / 2, ks), idesc, ks > 0);
-    t_issue = clock64();
-    mma_commit(&bar_x);
-    mbar_wait(&bar_x, 1, ctx, 9);
-    t1 = clock64();
-    p.c[128 * 128 + 6] = float(t_issue - t0);
-    p.c[128 * 128 + 7] = float(t1 - t0);
-    // 4 x 8 MMAs back to back
-    t0 = clock64();
-    for (int rep = 0; rep < 4; ++rep)
-      for (int ks = 0; ks < 8; ++ks)
-        mma_ss(tmem, sdesc_kmajor(a_addr, kTile / 2, ks), sdesc_kmajor(b_addr, kTile / 2, ks), idesc, ks > 0);
-    t_issue = clock64();
-    mma_commit(&bar_x);
-    mbar_wait(&bar_x, 0, ctx, 9);
-    t1 = clock64();
-    p.c[128 * 128 + 8] = float(t_issue - t0);
-    p.c[128 * 128 + 9] = float(t1 - t0);
-    // raw barrier polls on a completed phase (bar_load, parity 0), one by one
-    for (int i = 0; i < 4; ++i) {
-      t0 = clock64();
-      const bool a = mbar_try_wait(&bar_load, 0);
-      t1 = clock64();
-      p.c[128 * 128 + 16 + i] = float(t1 - t0) + (a ? 0.f : 1000000.f);
-    }
-    for (int i = 0; i < 4; ++i) {
-      uint32_t okv;
-      t0 = clock64();
-      asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.relaxed.cta.shared::cta.b64 P, [%1], %2;\nselp.b32 %0, 1, 0, P;\n}"
-                   : "=r"(okv) : "r"(smem_u32(&bar_load)), "r"(0) : "memory");
-      t1 = clock64();
-      p.c[128 * 128 + 20 + i] = float(t1 - t0) + (okv ? 0.f : 1000000.f);
-    }
-    for (int i = 0; i < 4; ++i) {
-      uint32_t okv;
-      t0 = clock64();
-      asm volatile("{\n.reg .pred P;\nmbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.b32 %0, 1, 0, P;\n}"
-                   : "=r"(okv) : "r"(smem_u32(&bar_load)), "r"(0) : "memory");
-      t1 = clock64();
-      p.c[128 * 128 + 24 + i] = float(t1 - t0) + (okv ? 0.f : 1000000.f);
-    }
-    for (int i = 0; i < 4; ++i) {
-      t0 = clock64();
-      const bool a = mbar_wait(&bar_load, 0, ctx, 9);
-      t1 = clock64();
-      p.c[128 * 128 + 28 + i] = float(t1 - t0) + (a ? 0.f : 1000000.f);
-    }
-    {
-      volatile uint32_t* sp = reinterpret_cast<volatile uint32_t*>(sC);
-      t0 = clock64();
-      uint32_t v = sp[0];
-      t1 = clock64();
-      p.c[128 * 128 + 32] = float(t1 - t0) + (v == 0x12345 ? 1.f : 0.f);
-    }
-    t0 = clock64();
-    fence_proxy_async_smem();
-    t1 = clock64();
-    p.c[128 * 128 + 11] = float(t1 - t0);
-    t0 = clock64();
-    tc_fence_before();
-    tc_fence_after();
-    t1 = clock64();
-    p.c[128 * 128 + 12] = float(t1 - t0);
-  }
-  __syncwarp();
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
