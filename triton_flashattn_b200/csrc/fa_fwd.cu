@@ -1,13 +1,14 @@
 // Forward attention kernel for sm_100a.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
-// 128 keys.  Roles (608 threads):
+// 128 keys.  Roles (640 threads):
 //   warps 0-15 softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
 //              lanes) and the 32-key quarter (w>>2) of every block; the four
 //              quarters of a row exchange partial maxima through shared memory
-//   warp 16    TMA producer (one elected lane): Q once, K / V rings, bias ring
+//   warp 16    TMA producer (one elected lane): Q once, K / V rings
 //   warp 17    MMA issuer for S = Q K^T (one lane), tensor-memory owner
 //   warp 18    MMA issuer for O += P V (one lane)
+//   warp 19    TMA producer of the bias / mask ring (one lane)
 // A barrier operation answers after ~200 cycles on this GPU; two issuers keep the
 // tensor pipe fed while one of them waits, and barriers are polled ahead of use.
 // Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
@@ -67,7 +68,7 @@ struct FwdSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(608, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
@@ -137,12 +138,9 @@ __global__ void __launch_bounds__(608, 1) fwd_kernel(const __grid_constant__ Fwd
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
-      if (BIAS != 0) tma_prefetch_desc(&p.map_bias);
-      const uint64_t pol_stream = policy_evict_first();
       mbar_expect_tx(&q_full, L::kTile);
       for (int kb = 0; kb < KB; ++kb)
         tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &q_full, kb * 64, h, m0, b);
-      uint32_t unit = 0;
       bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j & 1;
@@ -153,21 +151,6 @@ __global__ void __launch_bounds__(608, 1) fwd_kernel(const __grid_constant__ Fwd
         for (int kb = 0; kb < KB; ++kb)
           tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
                       n0, b);
-        if (BIAS != 0) {
-          // 16 KB units: 16-bit bias -> one per 64-key column half ([128 rows][64 keys]);
-          // byte mask -> one per block ([128 rows][128 keys]) shared by both halves
-          constexpr int kUnits = BIAS == 1 ? 2 : 1;
-          for (int u = 0; u < kUnits && ok; ++u, ++unit) {
-            const int bs = unit % NB;
-            const uint32_t use = unit / NB;
-            if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, j);
-            if (!ok) break;
-            mbar_expect_tx(&bias_full[bs], kBlk);
-            tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs],
-                             n0 + u * 64, m0, h * p.bias_h_mul, b * p.bias_b_mul, pol_stream);
-          }
-          if (!ok) break;
-        }
         if (j >= 2) ok = mbar_wait(&v_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
         if (!ok) break;
         mbar_expect_tx(&v_full[st], L::kTile);
@@ -227,6 +210,34 @@ __global__ void __launch_bounds__(608, 1) fwd_kernel(const __grid_constant__ Fwd
       }
     }
     __syncwarp();
+  } else if (warp == 19) {
+    // ------------------------------------------------------------ bias producer
+    // Its own thread: the bias ring is the HBM-latency-critical stream and must not
+    // queue behind the K / V ring's waits.
+    if (BIAS != 0 && lane == 0 && live) {
+      tma_prefetch_desc(&p.map_bias);
+      const uint64_t pol_stream = policy_evict_first();
+      uint32_t unit = 0;
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int n0 = j * 128;
+        {
+          // 16 KB units: 16-bit bias -> one per 64-key column half ([128 rows][64 keys]);
+          // byte mask -> one per block ([128 rows][128 keys]) shared by both halves
+          constexpr int kUnits = BIAS == 1 ? 2 : 1;
+          for (int u = 0; u < kUnits && ok; ++u, ++unit) {
+            const int bs = unit % NB;
+            const uint32_t use = unit / NB;
+            if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, j);
+            if (!ok) break;
+            mbar_expect_tx(&bias_full[bs], kBlk);
+            tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs],
+                             n0 + u * 64, m0, h * p.bias_h_mul, b * p.bias_b_mul, pol_stream);
+          }
+          if (!ok) break;
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------- softmax
     // thread = (query row r, key quarter qt): 32 of the 128 scores of the row per block
@@ -436,7 +447,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 608, L::kDynamic, stream>>>(fp);
+  kern<<<grid, 640, L::kDynamic, stream>>>(fp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 
