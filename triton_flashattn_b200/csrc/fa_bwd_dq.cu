@@ -2,8 +2,9 @@
 //
 // (1) dq_recompute_kernel -- general path (no bias, bool mask, float bias).
 // One CTA owns 128 query rows of one (batch, head) and walks the key blocks.
-// Roles (576 threads): warps 0-15 row threads (lanes 32*(w&3).., key quarter w>>2),
-// warp 16 TMA producer, warp 17 MMA issuer and tensor-memory owner.  Per key block:
+// Roles (608 threads): warps 0-15 row threads (lanes 32*(w&3).., key quarter w>>2),
+// warp 16 TMA producer, warp 17 MMA issuer for S and dP (tensor-memory owner),
+// warp 18 MMA issuer for dQ.  Per key block:
 //   S  = Q K_j^T, dP = dO V_j^T   (tensor memory)
 //   row threads: P = exp2(S*scale*log2e + bias*log2e - LSE2); dS = P*(dP - delta)
 //                -> 16-bit tile sDS in shared memory
@@ -61,7 +62,7 @@ struct DqSmem {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_constant__ DqParams p) {
+__global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_constant__ DqParams p) {
   using L = DqSmem<DP>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
     mbar_init(&qdo_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);  // S_j and dQ_j both read K_j
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
@@ -148,26 +149,24 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
       }
     }
   } else if (warp == 17) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ------------------------------------------------------- MMA issuer: S and dP
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
-      constexpr uint32_t idesc_dq = make_idesc(bf, false, true, 128, DP);
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
       const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
-      const uint32_t ds_addr = smem_u32(smem + L::kDs);
       const uint64_t q_km = make_sdesc(q_addr, 0, 1024), do_km = make_sdesc(do_addr, 0, 1024);
       const uint64_t k_km_0 = make_sdesc(k_addr, 0, 1024), k_km_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
-      const uint64_t k_mn_0 = make_sdesc(k_addr, kBlk, 1024), k_mn_1 = make_sdesc(k_addr + L::kTile, kBlk, 1024);
       const uint64_t v_km_0 = make_sdesc(v_addr, 0, 1024), v_km_1 = make_sdesc(v_addr + L::kTile, 0, 1024);
-      const uint64_t ds_km = make_sdesc(ds_addr, 0, 1024);
       auto issue_s = [&](int j) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, ((j & 1) ? k_km_1 : k_km_0), kBlk, kBlk, idesc_s, false);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, (j & 1) ? k_km_1 : k_km_0, kBlk, kBlk,
+                                          idesc_s, false);
         mma_commit(&s_full);
+        mma_commit(&k_empty[j & 1]);
       };
       auto issue_dp = [&](int j) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, ((j & 1) ? v_km_1 : v_km_0), kBlk, kBlk, idesc_s,
-                                          false);
+        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, (j & 1) ? v_km_1 : v_km_0, kBlk, kBlk,
+                                          idesc_s, false);
         mma_commit(&dp_full);
         mma_commit(&v_empty[j & 1]);
       };
@@ -182,26 +181,41 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
         tc_fence_after();
         issue_dp(0);
       }
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        if (j + 1 < nblk) {
-          const int st1 = (j + 1) & 1;
-          const uint32_t ph1 = ((j + 1) >> 1) & 1;
-          ok = mbar_wait(&k_full[st1], ph1, ctx, kSiteKFull, j + 1);
-          if (ok) ok = mbar_wait(&s_free, j & 1, ctx, kSiteSFree, j);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(j + 1);
-          ok = mbar_wait(&v_full[st1], ph1, ctx, kSiteVFull, j + 1);
-          if (ok) ok = mbar_wait(&dp_free, j & 1, ctx, kSiteDpFree, j);
-          if (!ok) break;
-          tc_fence_after();
-          issue_dp(j + 1);
-        }
-        ok = mbar_wait(&ds_ready, j & 1, ctx, kSiteDsReady, j);
+      for (int j = 0; j + 1 < nblk && ok; ++j) {
+        const int st1 = (j + 1) & 1;
+        const uint32_t ph1 = ((j + 1) >> 1) & 1;
+        const uint32_t pk = mbar_poll(&k_full[st1], ph1);
+        const uint32_t pv = mbar_poll(&v_full[st1], ph1);
+        ok = mbar_wait(&s_free, j & 1, ctx, kSiteSFree, j);
+        if (ok) ok = wait_polled(pk, &k_full[st1], ph1, ctx, kSiteKFull, j + 1);
         if (!ok) break;
         tc_fence_after();
-        issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, ((st) ? k_mn_1 : k_mn_0), kBlk, kBlk, idesc_dq, j > 0);
+        issue_s(j + 1);
+        ok = mbar_wait(&dp_free, j & 1, ctx, kSiteDpFree, j);
+        if (ok) ok = wait_polled(pv, &v_full[st1], ph1, ctx, kSiteVFull, j + 1);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dp(j + 1);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 18) {
+    // ------------------------------------------------------- MMA issuer: dQ += dS K
+    if (lane == 0 && live) {
+      constexpr uint32_t idesc_dq = make_idesc(P2::kIsBf16, false, true, 128, DP);
+      const uint32_t k_addr = smem_u32(smem + L::kK);
+      const uint64_t k_mn_0 = make_sdesc(k_addr, kBlk, 1024), k_mn_1 = make_sdesc(k_addr + L::kTile, kBlk, 1024);
+      const uint64_t ds_km = make_sdesc(smem_u32(smem + L::kDs), 0, 1024);
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t pk = mbar_poll(&k_full[st], (j >> 1) & 1);
+        ok = mbar_wait(&ds_ready, j & 1, ctx, kSiteDsReady, j);
+        if (ok) ok = wait_polled(pk, &k_full[st], (j >> 1) & 1, ctx, kSiteKFull, j);
+        if (!ok) break;
+        tc_fence_after();
+        issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, st ? k_mn_1 : k_mn_0, kBlk, kBlk, idesc_dq,
+                                      j > 0);
         mma_commit(&k_empty[st]);
         mma_commit(&dq_done);
       }
@@ -232,6 +246,8 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
 
       ok = wait_warp(&s_full, j & 1, ctx, kSiteSFull, j);
       if (!ok) break;
+      const uint32_t pdp = mbar_poll(&dp_full, j & 1);
+      const uint32_t pdq = j >= 1 ? mbar_poll(&dq_done, (j - 1) & 1) : 1u;
       tc_fence_after();
       float pr[32];
       tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
@@ -260,7 +276,7 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
           if (i >= limit) pr[i] = 0.f;
       }
 
-      ok = wait_warp(&dp_full, j & 1, ctx, kSiteDpFull, j);
+      ok = wait_warp_polled(pdp, &dp_full, j & 1, ctx, kSiteDpFull, j);
       if (!ok) break;
       tc_fence_after();
       uint32_t dsu[16];
@@ -279,7 +295,7 @@ __global__ void __launch_bounds__(576, 1) dq_recompute_kernel(const __grid_const
         }
       }
       if (j >= 1) {
-        ok = wait_warp(&dq_done, (j - 1) & 1, ctx, kSiteDqDone, j);
+        ok = wait_warp_polled(pdq, &dq_done, (j - 1) & 1, ctx, kSiteDqDone, j);
         if (!ok) break;
       }
 #pragma unroll
@@ -461,7 +477,7 @@ int launch_recompute(const DqParams& kp, dim3 grid, cudaStream_t stream) {
   static bool configured[64] = {};
   auto kern = dq_recompute_kernel<DP, T, BIAS>;
   if (int r = configure(kern, L::kDynamic, configured)) return r;
-  kern<<<grid, 576, L::kDynamic, stream>>>(kp);
+  kern<<<grid, 608, L::kDynamic, stream>>>(kp);
   return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
 }
 
