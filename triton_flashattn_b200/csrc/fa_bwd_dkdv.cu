@@ -364,7 +364,12 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const bool row_in = m0 + r < p.M;
       const float lse_raw = lse_next, delta_raw = delta_next;
       if (t + 1 < T_steps) prefetch(t + 1);
-      const uint32_t ps = mbar_poll(&s_full, t & 1);
+      // S_t and "dV_{t-1} has read P_{t-1}" are usually true by now: one combined look
+      uint32_t ps = 0, pdv = 1;
+      if (t >= 1)
+        mbar_poll2(&s_full, t & 1, &dv_done, (t - 1) & 1, ps, pdv);
+      else
+        ps = mbar_poll(&s_full, t & 1);
 
       // ---- P
       if (tid == 0) TR(0, t, 0);
@@ -379,9 +384,6 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free);
-      // barriers needed after the exponentials: ask now, the answers arrive meanwhile
-      const uint32_t pdv = t >= 1 ? mbar_poll(&dv_done, (t - 1) & 1) : 1u;
-      const uint32_t pdp = mbar_poll(&dp_full, t & 1);
       // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
       const float neg_lse = row_in ? -lse_raw : -INFINITY;
       const float delta_r = row_in ? delta_raw : 0.f;
@@ -425,8 +427,16 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       if (tid == 0) TR(0, t, 4);
 
       // ---- dS
-      const uint32_t pdk = t >= 1 ? mbar_poll(&dk_done, (t - 1) & 1) : 1u;
-      const uint32_t pst = p.write_dbias ? mbar_poll(&st_done, t & 1) : 1u;
+      // dP_t, "dK_{t-1} has read dS_{t-1}" and "its dbias store has": one combined look
+      uint32_t pdp = 0, pdk = 1, pst = 1;
+      if (t >= 1 && p.write_dbias)
+        mbar_poll3(&dp_full, t & 1, &dk_done, (t - 1) & 1, &st_done, t & 1, pdp, pdk, pst);
+      else if (t >= 1)
+        mbar_poll2(&dp_full, t & 1, &dk_done, (t - 1) & 1, pdp, pdk);
+      else if (p.write_dbias)
+        mbar_poll2(&dp_full, t & 1, &st_done, t & 1, pdp, pst);
+      else
+        pdp = mbar_poll(&dp_full, t & 1);
       ok = wait_warp_polled(pdp, &dp_full, t & 1, ctx, kSiteDpFull, t);
       if (!ok) break;
       if (tid == 0) TR(0, t, 5);

@@ -246,8 +246,6 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
 
       ok = wait_warp(&s_full, j & 1, ctx, kSiteSFull, j);
       if (!ok) break;
-      const uint32_t pdp = mbar_poll(&dp_full, j & 1);
-      const uint32_t pdq = j >= 1 ? mbar_poll(&dq_done, (j - 1) & 1) : 1u;
       tc_fence_after();
       float pr[32];
       tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
@@ -276,6 +274,11 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
           if (i >= limit) pr[i] = 0.f;
       }
 
+      uint32_t pdp = 0, pdq = 1;
+      if (j >= 1)
+        mbar_poll2(&dp_full, j & 1, &dq_done, (j - 1) & 1, pdp, pdq);
+      else
+        pdp = mbar_poll(&dp_full, j & 1);
       ok = wait_warp_polled(pdp, &dp_full, j & 1, ctx, kSiteDpFull, j);
       if (!ok) break;
       tc_fence_after();

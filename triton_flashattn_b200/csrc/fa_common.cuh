@@ -94,6 +94,41 @@ __device__ __forceinline__ uint32_t mbar_poll(uint64_t* bar, uint32_t parity) {
   return ok;
 }
 
+// Two / three phases looked at in one go: the barrier queries are issued back to back
+// and their answers (each ~200 cycles away) come back together, instead of one
+// round trip after the other.
+__device__ __forceinline__ void mbar_poll2(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1,
+                                           uint32_t& r0, uint32_t& r1) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P0, P1;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P0, [%2], %3;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P1, [%4], %5;\n"
+      "selp.b32 %0, 1, 0, P0;\n"
+      "selp.b32 %1, 1, 0, P1;\n"
+      "}\n"
+      : "=r"(r0), "=r"(r1)
+      : "r"(smem_u32(b0)), "r"(p0), "r"(smem_u32(b1)), "r"(p1)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_poll3(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1,
+                                           uint64_t* b2, uint32_t p2, uint32_t& r0, uint32_t& r1,
+                                           uint32_t& r2) {
+  asm volatile(
+      "{\n"
+      ".reg .pred P0, P1, P2;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P0, [%3], %4;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P1, [%5], %6;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P2, [%7], %8;\n"
+      "selp.b32 %0, 1, 0, P0;\n"
+      "selp.b32 %1, 1, 0, P1;\n"
+      "selp.b32 %2, 1, 0, P2;\n"
+      "}\n"
+      : "=r"(r0), "=r"(r1), "=r"(r2)
+      : "r"(smem_u32(b0)), "r"(p0), "r"(smem_u32(b1)), "r"(p1), "r"(smem_u32(b2)), "r"(p2)
+      : "memory");
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -251,14 +251,18 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
     const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
     const float scale_log2 = p.sm_scale * kLog2e;
     uint32_t unit = BIAS == 1 ? (qt >> 1) : 0;  // 16-bit bias: units hf, hf+2, ...; mask: one per block
-    uint32_t ps_next = 0;  // early look at the barrier of the next block's scores
     for (int j = 0; j < nblk && ok; ++j) {
       const int st = j & 1;
       const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
       if (tid == 0) TR(0, j, 0);
-      // barriers of this step that are probably complete already: ask first, use later
-      const uint32_t pbias = BIAS != 0 ? mbar_poll(&bias_full[unit % NB], (unit / NB) & 1) : 1u;
-      ok = wait_warp_polled(ps_next, &s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
+      // the scores and the bias unit of this step are usually there already: one combined
+      // look at both barriers (their answers travel together), blocking waits only if not
+      uint32_t ps = 1, pbias = 1;
+      if (BIAS != 0)
+        mbar_poll2(&s_full[st], (j >> 1) & 1, &bias_full[unit % NB], (unit / NB) & 1, ps, pbias);
+      else
+        ps = mbar_poll(&s_full[st], (j >> 1) & 1);
+      ok = wait_warp_polled(ps, &s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
       if (tid == 0) TR(0, j, 1);
       tc_fence_after();
@@ -339,10 +343,15 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       if (tid == 0) TR(0, j, 4);
       xchg[j & 1][qt][r] = mx;
-      const uint32_t ppv = j > 0 ? mbar_poll(&pv_done, (j - 1) & 1) : 1u;
       __syncwarp();
       if (lane == 0) mbar_arrive(row_bar);
-      ok = wait_warp(row_bar, j & 1, ctx, kSitePair, j);
+      // the exchange barrier and "P_{j-1} V_{j-1} is through" are looked at together
+      uint32_t prow = 0, ppv = 1;
+      if (j > 0)
+        mbar_poll2(row_bar, j & 1, &pv_done, (j - 1) & 1, prow, ppv);
+      else
+        prow = mbar_poll(row_bar, j & 1);
+      ok = wait_warp_polled(prow, row_bar, j & 1, ctx, kSitePair, j);
       if (!ok) break;
       mx = fmaxf(fmaxf(xchg[j & 1][0][r], xchg[j & 1][1][r]),
                  fmaxf(xchg[j & 1][2][r], xchg[j & 1][3][r])) * mul;  // block maximum, log2 domain
