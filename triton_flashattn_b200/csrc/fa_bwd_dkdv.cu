@@ -348,9 +348,16 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     auto prefetch = [&](int t) {
       const int m = (i_start + t) * 128 + r;
       const bool row_ok = m < p.M;
-      if (BIAS != 0)
+      if (BIAS == 1 && p.bias_vec32 && col0 + 32 <= p.N) {
+        // warp-wide: one request per line, then a shuffle pass (see load_bias_rows_paired)
+        const int mrow0 = (i_start + t) * 128 + (warp & 3) * 32;
+        if constexpr (BIAS == 1)
+          load_bias_rows_paired(bnext, p.bias, bias_bh + (int64_t)mrow0 * p.bias_sM, p.bias_sM,
+                                p.M - mrow0, col0, lane);
+      } else if (BIAS != 0) {
         load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N,
                             p.bias_vec32 != 0);
+      }
       // clamped address: the value of a row beyond M is replaced when it is used
       const int mc = row_ok ? m : p.M - 1;
       lse_next = __ldg(p.lse + (int64_t)bh * p.M + mc);
@@ -361,6 +368,9 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     for (int t = 0; t < T_steps && ok; ++t) {
       const int m0 = (i_start + t) * 128;
       BiasRegs<BIAS> bcur = bnext;
+      if constexpr (BIAS == 1) {
+        if (p.bias_vec32 && col0 + 32 <= p.N) redistribute_bias_rows(bcur, lane);
+      }
       const bool row_in = m0 + r < p.M;
       const float lse_raw = lse_next, delta_raw = delta_next;
       if (t + 1 < T_steps) prefetch(t + 1);
