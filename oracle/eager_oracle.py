@@ -72,8 +72,13 @@ def attention_forward(q, k, v, bias=None, causal=False, sm_scale=None):
     return out, lse2, p
 
 
-def attention_backward(q, k, v, bias, causal, sm_scale, do):
-    """Closed-form fp32 backward; returns dict(out, dq, dk, dv, dbias, delta, lse2)."""
+def attention_backward(q, k, v, bias, causal, sm_scale, do, o_saved=None):
+    """Closed-form fp32 backward; returns dict(out, dq, dk, dv, dbias, delta, lse2).
+
+    `o_saved`: the 16-bit output tensor a forward pass actually saved.  The backward of
+    the reference reads that tensor to form delta, so when the backward of another
+    implementation is checked it should be given that implementation's own saved output
+    (a one-unit-in-the-last-place difference in `o` moves delta by ~sqrt(D) units)."""
     D = q.shape[-1]
     sm_scale = D ** -0.5 if sm_scale is None else sm_scale
     out, lse2, p = attention_forward(q, k, v, bias, causal, sm_scale)
@@ -83,7 +88,10 @@ def attention_backward(q, k, v, bias, causal, sm_scale, do):
     kf = k.float().transpose(1, 2)
     # The reference saves `o` in q's dtype (FA:653) and its preprocess kernel reads that
     # tensor (FA:207-219), so delta is formed from the ROUNDED output.
-    o_saved = out.to(q.dtype).float() if q.dtype in (torch.float16, torch.bfloat16) else out
+    if o_saved is not None:
+        o_saved = o_saved.float()
+    else:
+        o_saved = out.to(q.dtype).float() if q.dtype in (torch.float16, torch.bfloat16) else out
     delta = (o_saved.transpose(1, 2) * dof).sum(-1)  # (B, H, M)
     dv = torch.matmul(p.transpose(-1, -2), dof)
     dp = torch.matmul(dof, vf.transpose(-1, -2))

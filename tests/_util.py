@@ -65,7 +65,7 @@ def check_case(B, M, N, H, D, dtype, bias_kind, causal, seed=0, sm_scale=None, b
                tol_mult=1.0, trainable_bias=True, verbose=True):
     q, k, v, bias, do = make_inputs(B, M, N, H, D, dtype, bias_kind, seed, bias_scale=bias_scale)
     ours = run_ours(q, k, v, bias, causal, sm_scale, do, trainable_bias)
-    ref = oracle.attention_backward(q, k, v, bias, causal, sm_scale, do)
+    ref = oracle.attention_backward(q, k, v, bias, causal, sm_scale, do, o_saved=ours["out"])
     errs = errors(ours, ref, dtype)
     tol = TOL[dtype] * tol_mult
     if verbose:

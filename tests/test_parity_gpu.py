@@ -225,7 +225,8 @@ def test_benchmark_config_shapes(cfg, device_ok):
         for h in range(H):
             sl = lambda t: t[b:b + 1, :, h:h + 1]
             bb = None if bias is None else bias[b:b + 1, h:h + 1]
-            ref = oracle.attention_backward(sl(q), sl(k), sl(v), bb, causal, None, sl(do))
+            ref = oracle.attention_backward(sl(q), sl(k), sl(v), bb, causal, None, sl(do),
+                                            o_saved=sl(ours["out"]))
             part = {n: sl(t) for n, t in ours.items() if n != "dbias"}
             if "dbias" in ours:
                 part["dbias"] = ours["dbias"][b:b + 1, h:h + 1]
