@@ -66,6 +66,17 @@ def test_longer_sequence_bf16(device_ok):
     check_case(1, 1024, 1024, 2, 64, BF, None, True, seed=5)
 
 
+@pytest.mark.parametrize("max_ctas", ["1", "3", "5"])
+@pytest.mark.parametrize("D,bias_kind,causal", [(128, "float", False), (128, "float", True), (64, None, True),
+                                                (128, "bool", True), (64, "float", False)])
+def test_many_tiles_per_persistent_cta(max_ctas, D, bias_kind, causal, device_ok, monkeypatch):
+    """The kernels are persistent (one CTA per SM walks several tiles, carrying ring stages and
+    barrier phases across tile boundaries).  FA_MAX_CTAS caps the grid so that a small problem
+    exercises many tile boundaries per CTA, including odd tile counts and ragged edges."""
+    monkeypatch.setenv("FA_MAX_CTAS", max_ctas)
+    check_case(2, 3 * 128 + 40, 5 * 128 - 9, 3, D, BF, bias_kind, causal, seed=21, bias_scale=0.5)
+
+
 def test_non_trainable_float_bias(device_ok):
     check_case(1, 256, 256, 2, 128, BF, "float", True, seed=6, trainable_bias=False)
 

@@ -1,5 +1,6 @@
 // extern "C" entry points of libfa_sm100.so: argument validation, tensor-map
 // encoding, the per-device status word and dispatch to the kernel launchers.
+#include <cstdlib>
 #include <mutex>
 
 #include "fa_host.cuh"
@@ -70,6 +71,24 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, const uint6
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FA_OK : FA_ERR_CUDA;
+}
+
+int persistent_grid(int n_tiles) {
+  static int sm_count[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = 0;
+  if (dev >= 0 && dev < kMaxDevices) sms = sm_count[dev];
+  if (sms <= 0) {
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+    if (dev >= 0 && dev < kMaxDevices) sm_count[dev] = sms;
+  }
+  if (const char* cap = getenv("FA_MAX_CTAS")) {
+    const int c = atoi(cap);
+    if (c > 0 && c < sms) sms = c;
+  }
+  return n_tiles < sms ? (n_tiles < 1 ? 1 : n_tiles) : sms;
 }
 
 int* device_status_ptr(int device) {

@@ -147,19 +147,34 @@ struct WaitCtx {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
 // Returns true when the phase completed, false when the kernel must bail out.
+#if defined(FA_TRACE) || defined(FA_WAITLOG_ON)
+static __device__ int g_fa_waitlog[1 + 64 * 6];  // lane 0 of each warp only
+static __device__ __noinline__ void waitlog(int site, int iter, int why) {
+  if (threadIdx.x & 31) return;
+  const int i = atomicAdd(&g_fa_waitlog[0], 1);
+  if (i < 64) {
+    int* e = &g_fa_waitlog[1 + i * 6];
+    e[0] = blockIdx.x; e[1] = threadIdx.x; e[2] = site; e[3] = iter; e[4] = why; e[5] = 0;
+  }
+}
+#define FA_WAITLOG(site, iter, why) waitlog(site, iter, why)
+#else
+#define FA_WAITLOG(site, iter, why) do {} while (0)
+#endif
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
                                             int site, int iter) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.abort_flag) return false;
+    if (*ctx.abort_flag) { FA_WAITLOG(site, iter, 2); return false; }
     if ((++spins & 63u) == 0) {
       if (*reinterpret_cast<volatile int*>(ctx.status) != 0) {
         *ctx.abort_flag = 1;
         return false;
       }
       if (global_timer_ns() - t0 > kWaitLimitNs) {
+        FA_WAITLOG(site, iter, 1);
         *ctx.abort_flag = 1;
         if (atomicCAS(ctx.status, 0, kStatusWaitTimeout) == 0) {
           ctx.status[1] = ctx.kernel_id;
@@ -539,6 +554,7 @@ __device__ __forceinline__ void ldg256(const void* ptr, uint32_t* r) {
 // ----------------------------------------------------------------------------
 // helpers shared by the attention kernels
 // ----------------------------------------------------------------------------
+
 constexpr int kBlk = 128 * 128;  // bytes of one [128][64] 16-bit tile block (also [128][128] u8)
 
 // All lanes wait, then agree: a warp leaves its loop as a whole.

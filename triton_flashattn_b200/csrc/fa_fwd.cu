@@ -1,11 +1,14 @@
 // Forward attention kernel for sm_100a.
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the key blocks of
-// 128 keys.  Roles (640 threads):
+// Persistent kernel, one CTA per SM.  A tile is 128 query rows of one (batch,
+// head); a CTA walks its tiles one after the other and, inside a tile, the key
+// blocks of 128 keys.  Ring stages, tensor-memory buffers and barrier phases run on
+// from tile to tile, so the next tile's Q / K / V / bias loads and its first
+// Q K^T product overlap the current tile's epilogue.  Roles (640 threads):
 //   warps 0-15 softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
 //              lanes) and the 32-key quarter (w>>2) of every block; the four
 //              quarters of a row exchange partial maxima through shared memory
-//   warp 16    TMA producer (one elected lane): Q once, K / V rings
+//   warp 16    TMA producer (one elected lane): Q per tile, K / V rings
 //   warp 17    MMA issuer for S = Q K^T (one lane), tensor-memory owner
 //   warp 18    MMA issuer for O += P V (one lane)
 //   warp 19    TMA producer of the bias / mask ring (one lane)
@@ -48,11 +51,12 @@ struct FwdParams {
   int H, M, N, D;
   int causal;
   int bias_b_mul, bias_h_mul;
+  int n_mblk, n_tiles;  // query blocks per (batch, head); tiles = n_mblk * B * H
   float sm_scale;
 };
 
 enum FwdSite { kSiteQ = 1, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty, kSiteSFull,
-               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue, kSitePair };
+               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue, kSitePair, kSiteQEmpty, kSitePvDoneQK };
 
 template <int DP, int BIAS>
 struct FwdSmem {
@@ -81,8 +85,8 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full,
-      pv_done;
+  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
+      p_full, pv_done[2];
   __shared__ uint64_t bias_full[4], bias_empty[4], row_bars[4];
   __shared__ float xchg[2][4][128];  // [step parity][key quarter][row]: partial row maxima / sums
   __shared__ uint32_t tmem_slot;
@@ -91,20 +95,34 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int m_block = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
-  const int bh = blockIdx.y;
-  const int b = bh / p.H;
-  const int h = bh - b * p.H;
-  const int m0 = m_block * 128;
-
-  int nblk = (p.N + 127) >> 7;
-  if (p.causal) nblk = min(nblk, m_block + 1);
+  // Persistent CTA: it walks tiles (tile = 128 query rows of one (batch, head)) and all
+  // roles keep running counters, so the rings, the tensor-memory buffers and every barrier
+  // phase carry on from one tile to the next: the loads and the first products of the next
+  // tile overlap the epilogue of the current one.
+  // Schedule: tiles are numbered (batch*head)-major; CTA c takes units c, c+G, c+2G, ...
+  // so that the CTAs running at the same time work on neighbouring tiles and share K / V in
+  // L2.  A unit is one tile, or - causal - two consecutive entries of the per-(batch, head)
+  // order [last, first, last-1, first+1, ...]: a heavy and a light block, so every unit
+  // carries about the same number of key blocks.
+  const int nblk_all = (p.N + 127) >> 7;
+  const int sched_sh = p.causal ? 1 : 0;
+  auto tile_at = [&](int it, int& bh, int& m_block, int& nblk) -> bool {
+    const int u = static_cast<int>(blockIdx.x) + (it >> sched_sh) * static_cast<int>(gridDim.x);
+    const int k = (u << sched_sh) + (it & sched_sh);
+    if (k >= p.n_tiles) return false;
+    bh = k / p.n_mblk;
+    const int pos = k - bh * p.n_mblk;
+    m_block = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_mblk - 1 - (pos >> 1)) : pos;
+    nblk = p.causal ? min(nblk_all, m_block + 1) : nblk_all;
+    return true;
+  };
 
   WaitCtx ctx{&abort_flag, p.status, 1};
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
+    mbar_init(&q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -113,7 +131,8 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       mbar_init(&s_full[i], 1);
     }
     mbar_init(&p_full, 16);
-    mbar_init(&pv_done, 1);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bias_full[i], 1);
       mbar_init(&bias_empty[i], BIAS == 2 ? 16 : 8);
@@ -138,25 +157,35 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
-      mbar_expect_tx(&q_full, L::kTile);
-      for (int kb = 0; kb < KB; ++kb)
-        tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &q_full, kb * 64, h, m0, b);
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        const int n0 = j * 128;
-        if (j >= 2) ok = mbar_wait(&k_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+      uint32_t gj = 0;  // key blocks issued so far, over all tiles
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
+        // the single Q tile is free once every Q K^T product of the previous tile is through
+        if (it >= 1) ok = mbar_wait(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&k_full[st], L::kTile);
+        mbar_expect_tx(&q_full, L::kTile);
         for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
-                      n0, b);
-        if (j >= 2) ok = mbar_wait(&v_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
-        if (!ok) break;
-        mbar_expect_tx(&v_full[st], L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
-                      n0, b);
+          tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &q_full, kb * 64, h, m0, b);
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const int n0 = j * 128;
+          if (g >= 2) ok = mbar_wait(&k_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+          if (!ok) break;
+          mbar_expect_tx(&k_full[st], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64,
+                        h, n0, b);
+          if (g >= 2) ok = mbar_wait(&v_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
+          if (!ok) break;
+          mbar_expect_tx(&v_full[st], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64,
+                        h, n0, b);
+        }
+        gj += nblk;
       }
     }
   } else if (warp == 17) {
@@ -168,21 +197,33 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       const uint32_t k_addr = smem_u32(smem + L::kK);
       const uint64_t q_desc = make_sdesc(q_addr, 0, 1024);
       const uint64_t k_desc_0 = make_sdesc(k_addr, 0, 1024), k_desc_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
-      bool ok = mbar_wait(&q_full, 0, ctx, kSiteQ, 0);
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t pk = mbar_poll(&k_full[st], (j >> 1) & 1);
-        // S_j overwrites the columns that held P_{j-2}: P_{j-2} V_{j-2} must be through
-        if (j >= 2) ok = mbar_wait(&pv_done, (j - 2) & 1, ctx, kSitePvDone, j);
-        if (ok) ok = wait_polled(pk, &k_full[st], (j >> 1) & 1, ctx, kSiteKFull, j);
-        if (!ok) break;
-        TR(1, j, 1);
-        tc_fence_after();
-        issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc, st ? k_desc_1 : k_desc_0,
-                                           kBlk, kBlk, idesc_qk, false);
-        mma_commit(&s_full[st]);
-        mma_commit(&k_empty[st]);
-        TR(1, j, 2);
+      bool ok = true;
+      uint32_t gj = 0;
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const uint32_t pk = mbar_poll(&k_full[st], (g >> 1) & 1);
+          // S_g overwrites the columns that held P_{g-2}: P_{g-2} V_{g-2} must be through.
+          // One barrier per S buffer: its next completion (P_g V_g) needs this very S_g, so
+          // the barrier can never run two phases ahead of this wait, however long the issuer
+          // sat in another wait (a new tile's Q) in between.
+          if (g >= 2)
+            ok = mbar_wait(&pv_done[st], ((g >> 1) - 1) & 1, ctx, kSitePvDoneQK, j);
+          if (ok && j == 0) ok = mbar_wait(&q_full, it & 1, ctx, kSiteQ, it);
+          if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
+          if (!ok) break;
+          TR(1, g, 1);
+          tc_fence_after();
+          issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc,
+                                             st ? k_desc_1 : k_desc_0, kBlk, kBlk, idesc_qk, false);
+          mma_commit(&s_full[st]);
+          mma_commit(&k_empty[st]);
+          if (j == nblk - 1) mma_commit(&q_empty);
+          TR(1, g, 2);
+        }
+        gj += nblk;
       }
     }
     __syncwarp();
@@ -194,19 +235,27 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       const uint32_t v_addr = smem_u32(smem + L::kV);
       const uint64_t v_desc_0 = make_sdesc(v_addr, kBlk, 1024), v_desc_1 = make_sdesc(v_addr + L::kTile, kBlk, 1024);
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t pv = mbar_poll(&v_full[st], (j >> 1) & 1);
-        ok = mbar_wait(&p_full, j & 1, ctx, kSitePFull, j);
-        if (ok) ok = wait_polled(pv, &v_full[st], (j >> 1) & 1, ctx, kSiteVFull, j);
-        if (!ok) break;
-        TR(1, j, 4);
-        tc_fence_after();
-        issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, st ? v_desc_1 : v_desc_0, kBlk,
-                               idesc_pv, j > 0);
-        mma_commit(&v_empty[st]);
-        mma_commit(&pv_done);
-        TR(1, j, 5);
+      uint32_t gj = 0;
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const uint32_t pv = mbar_poll(&v_full[st], (g >> 1) & 1);
+          // P_g of a new tile is only announced after all sixteen softmax warps have read
+          // the previous tile's O, so the first product of a tile may overwrite it
+          ok = mbar_wait(&p_full, g & 1, ctx, kSitePFull, j);
+          if (ok) ok = wait_polled(pv, &v_full[st], (g >> 1) & 1, ctx, kSiteVFull, j);
+          if (!ok) break;
+          TR(1, g, 4);
+          tc_fence_after();
+          issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, st ? v_desc_1 : v_desc_0,
+                                 kBlk, idesc_pv, j > 0);
+          mma_commit(&v_empty[st]);
+          mma_commit(&pv_done[st]);
+          TR(1, g, 5);
+        }
+        gj += nblk;
       }
     }
     __syncwarp();
@@ -219,9 +268,11 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       const uint64_t pol_stream = policy_evict_first();
       uint32_t unit = 0;
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int n0 = j * 128;
-        {
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
+        for (int j = 0; j < nblk && ok; ++j) {
+          const int n0 = j * 128;
           // 16 KB units: 16-bit bias -> one per 64-key column half ([128 rows][64 keys]);
           // byte mask -> one per block ([128 rows][128 keys]) shared by both halves
           constexpr int kUnits = BIAS == 1 ? 2 : 1;
@@ -234,7 +285,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
             tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs],
                              n0 + u * 64, m0, h * p.bias_h_mul, b * p.bias_b_mul, pol_stream);
           }
-          if (!ok) break;
         }
       }
     }
@@ -245,31 +295,38 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
     const int qt = warp >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     uint64_t* row_bar = &row_bars[warp & 3];  // shared by the four warps that own the same rows
-    float m_used = -INFINITY;                 // running maximum, log2 domain
-    float l = 0.f;                            // partial row sum over this thread's keys
     bool ok = live;
     const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
     const float scale_log2 = p.sm_scale * kLog2e;
-    uint32_t unit = BIAS == 1 ? (qt >> 1) : 0;  // 16-bit bias: units hf, hf+2, ...; mask: one per block
+    uint32_t gj = 0;  // key blocks done so far, over all tiles (ring stages and barrier phases)
+    int bh, m_block, nblk;
+    for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+    const int m0 = m_block * 128;
+    float m_used = -INFINITY;  // running maximum, log2 domain
+    float l = 0.f;             // partial row sum over this thread's keys
     for (int j = 0; j < nblk && ok; ++j) {
-      const int st = j & 1;
+      const uint32_t g = gj + j;
+      const int st = g & 1;
+      const uint32_t gx = g + it;  // quarter exchanges so far: one per block, one per tile
+      // bias unit of this step: 16-bit bias -> two per block (this quarter's half); mask -> one
+      const uint32_t unit = BIAS == 1 ? 2 * g + (qt >> 1) : g;
       const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
-      if (tid == 0) TR(0, j, 0);
+      if (tid == 0) TR(0, g, 0);
       // the scores and the bias unit of this step are usually there already: one combined
       // look at both barriers (their answers travel together), blocking waits only if not
       uint32_t ps = 1, pbias = 1;
       if (BIAS != 0)
-        mbar_poll2(&s_full[st], (j >> 1) & 1, &bias_full[unit % NB], (unit / NB) & 1, ps, pbias);
+        mbar_poll2(&s_full[st], (g >> 1) & 1, &bias_full[unit % NB], (unit / NB) & 1, ps, pbias);
       else
-        ps = mbar_poll(&s_full[st], (j >> 1) & 1);
-      ok = wait_warp_polled(ps, &s_full[st], (j >> 1) & 1, ctx, kSiteSFull, j);
+        ps = mbar_poll(&s_full[st], (g >> 1) & 1);
+      ok = wait_warp_polled(ps, &s_full[st], (g >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
-      if (tid == 0) TR(0, j, 1);
+      if (tid == 0) TR(0, g, 1);
       tc_fence_after();
       float s[32];
       tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 32), reinterpret_cast<uint32_t*>(s));
       tmem_ld_wait();
-      if (tid == 0) TR(0, j, 2);
+      if (tid == 0) TR(0, g, 2);
       // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
       // Without a bias (and a positive scale) the raw q.k is kept and the scale is
       // folded into the exponent below.
@@ -317,7 +374,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bias_empty[bs]);
-        unit += BIAS == 1 ? 2 : 1;
       }
       // ---- bounds and causal masks (only on blocks that need them)
       if ((n0 + 32 > p.N) || (p.causal && n0 + 31 > m0)) {
@@ -327,7 +383,7 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         for (int i = 0; i < 32; ++i)
           if (i >= limit) s[i] = -INFINITY;
       }
-      if (tid == 0) TR(0, j, 3);
+      if (tid == 0) TR(0, g, 3);
       // ---- row maximum over this quarter, exchanged with the three partner quarters
       float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
       float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
@@ -341,29 +397,29 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       mx0 = max3(mx0, s[28], s[29]);  // 12 + 2*8 = 28 consumed; 28..31 left
       mx1 = max3(mx1, s[30], s[31]);
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      if (tid == 0) TR(0, j, 4);
-      xchg[j & 1][qt][r] = mx;
+      if (tid == 0) TR(0, g, 4);
+      xchg[gx & 1][qt][r] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(row_bar);
       // the exchange barrier and "P_{j-1} V_{j-1} is through" are looked at together
       uint32_t prow = 0, ppv = 1;
       if (j > 0)
-        mbar_poll2(row_bar, j & 1, &pv_done, (j - 1) & 1, prow, ppv);
+        mbar_poll2(row_bar, gx & 1, &pv_done[st ^ 1], ((g - 1) >> 1) & 1, prow, ppv);
       else
-        prow = mbar_poll(row_bar, j & 1);
-      ok = wait_warp_polled(prow, row_bar, j & 1, ctx, kSitePair, j);
+        prow = mbar_poll(row_bar, gx & 1);
+      ok = wait_warp_polled(prow, row_bar, gx & 1, ctx, kSitePair, j);
       if (!ok) break;
-      mx = fmaxf(fmaxf(xchg[j & 1][0][r], xchg[j & 1][1][r]),
-                 fmaxf(xchg[j & 1][2][r], xchg[j & 1][3][r])) * mul;  // block maximum, log2 domain
-      if (tid == 0) TR(0, j, 5);
+      mx = fmaxf(fmaxf(xchg[gx & 1][0][r], xchg[gx & 1][1][r]),
+                 fmaxf(xchg[gx & 1][2][r], xchg[gx & 1][3][r])) * mul;  // block maximum, log2 domain
+      if (tid == 0) TR(0, g, 5);
       const bool need = mx > m_used + 8.0f;
       const bool any_need = __any_sync(0xffffffffu, need);
       // O may only be touched once P_{j-1} V_{j-1} has completed.
       if (j > 0) {
-        ok = wait_warp_polled(ppv, &pv_done, (j - 1) & 1, ctx, kSitePvDone, j);
+        ok = wait_warp_polled(ppv, &pv_done[st ^ 1], ((g - 1) >> 1) & 1, ctx, kSitePvDone, j);
         if (!ok) break;
       }
-      if (tid == 0) TR(0, j, 6);
+      if (tid == 0) TR(0, g, 6);
       if (any_need) {
         const float m_new = need ? mx : m_used;
         const float alpha = need ? ex2(m_used - m_new) : 1.0f;
@@ -379,7 +435,7 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           tmem_st_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
         }
       }
-      if (tid == 0) TR(0, j, 7);
+      if (tid == 0) TR(0, g, 7);
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
       uint32_t pk[16];
@@ -397,35 +453,42 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         pk[i + 1] = P2::pack(p2, p3);
       }
       l += (sum0 + sum1) + (sum2 + sum3);
-      if (tid == 0) TR(0, j, 8);
+      if (tid == 0) TR(0, g, 8);
       // P (16 bit) over the S columns: this quarter's 32 keys -> 16 packed columns
       tmem_st16(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 16), pk);
       tmem_st_wait();
-      if (tid == 0) TR(0, j, 9);
+      if (tid == 0) TR(0, g, 9);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-      if (tid == 0) TR(0, j, 10);
+      if (tid == 0) TR(0, g, 10);
     }
     // ---- epilogue: O / l -> global, log-sum-exp
-    if (ok) ok = wait_warp(&pv_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
+    if (!ok) break;
+    gj += nblk;
+    ok = wait_warp(&pv_done[(gj - 1) & 1], ((gj - 1) >> 1) & 1, ctx, kSiteEpilogue, nblk);
     // full row sum = sum of the four quarters
+    const uint32_t gx = gj + it;
     if (ok) {
-      xchg[nblk & 1][qt][r] = l;
+      xchg[gx & 1][qt][r] = l;
       __syncwarp();
       if (lane == 0) mbar_arrive(row_bar);
-      ok = wait_warp(row_bar, nblk & 1, ctx, kSitePair, nblk);
+      ok = wait_warp(row_bar, gx & 1, ctx, kSitePair, nblk);
     }
     if (ok) {
-      l = (xchg[nblk & 1][0][r] + xchg[nblk & 1][1][r]) + (xchg[nblk & 1][2][r] + xchg[nblk & 1][3][r]);
+      l = (xchg[gx & 1][0][r] + xchg[gx & 1][1][r]) + (xchg[gx & 1][2][r] + xchg[gx & 1][3][r]);
       tc_fence_after();
       const int m = m0 + r;
+      const int b = bh / p.H, h = bh - b * p.H;
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM +
                 h * p.o_sH;
       uint32_t o[kQD];
       tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
       tmem_ld_wait();
+      // O is in registers: the next tile's first P V product may overwrite it (it is issued
+      // after all sixteen warps have announced that tile's first P)
+      tc_fence_before();
       if (m < p.M) {
 #pragma unroll
         for (int c = 0; c < kQD / 8; ++c) {
@@ -436,6 +499,7 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       if (qt == 0 && m < p.M)
         p.lse[(static_cast<int64_t>(bh)) * p.M + m] = l > 0.f ? m_used + log2f(l) : INFINITY;
     }
+    }  // tiles
   }
 
   tc_fence_before();
@@ -472,6 +536,12 @@ int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stre
 
 }  // namespace
 
+#if defined(FA_TRACE) || defined(FA_WAITLOG_ON)
+extern "C" int fa_debug_read_waitlog(int* out) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(out, g_fa_waitlog, sizeof(int) * (1 + 64 * 6)) == cudaSuccess ? 0 : 1;
+}
+#endif
 #ifdef FA_TRACE
 extern "C" int fa_debug_read_trace(long long* out, int n) {
   cudaDeviceSynchronize();
@@ -514,7 +584,9 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   fp.D = p.D;
   fp.causal = p.causal ? 1 : 0;
   fp.sm_scale = p.sm_scale;
-  const dim3 grid((p.M + 127) / 128, p.B * p.H);
+  fp.n_mblk = (p.M + 127) / 128;
+  fp.n_tiles = fp.n_mblk * p.B * p.H;
+  const dim3 grid(persistent_grid(p.causal ? (fp.n_tiles + 1) / 2 : fp.n_tiles));
   const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {
     return dp == 64 ? launch_bias<64, __nv_bfloat16>(fp, p.bias_kind, grid, stream)

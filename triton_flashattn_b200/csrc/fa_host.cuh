@@ -32,6 +32,12 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status);
 int launch_selftest(int mode, int dtype, const void* a, const void* b, void* c, cudaStream_t stream,
                     int* status);
 
+// Grid of a persistent kernel: one CTA per SM of the current device, never more than
+// there are work units.  The environment variable FA_MAX_CTAS (a positive integer, read at
+// every launch) lowers the cap; tests use it to make small problems walk many tiles
+// per CTA.
+int persistent_grid(int n_tiles);
+
 // Head dims are computed on a padded width: 16/32/64 -> 64, 128 -> 128.
 inline int padded_head_dim(int d) { return d <= 64 ? 64 : d; }
 
