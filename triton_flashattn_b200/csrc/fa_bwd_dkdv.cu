@@ -1,10 +1,15 @@
 // dK / dV (and dbias) kernel for sm_100a.
 //
-// One CTA owns 128 keys of one (batch, head) and walks the query blocks of 128
-// rows (only those at or below the diagonal when causal).  Roles (640 threads):
+// Persistent kernel, one CTA per SM.  A tile is 128 keys of one (batch, head); a CTA
+// walks its tiles one after the other and, inside a tile, the query blocks of 128 rows
+// (only those at or below the diagonal when causal).  Ring stages, tensor-memory buffers
+// and barrier phases run on from tile to tile, so the next tile's K / V / Q / dO loads,
+// its first S and dP products and its first bias rows overlap the current tile's
+// epilogue.  Roles (640 threads):
 //   warps 0-15 "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
 //              (query rows of the block) and on the 32-key column quarter (w>>2)
-//   warp 16    TMA producer (one lane): K, V once; Q ring (2), dO ring
+//   warp 16    TMA producer (one lane): K, V per tile; Q ring (2), dO ring; bias tiles
+//              are asked into L2 two steps ahead
 //   warp 17    MMA issuer for S and dP (one lane), tensor-memory owner
 //   warp 18    MMA issuer for dV and dK (one lane)
 //   warp 19    bulk tensor stores of the dS tile into dbias (one lane)
@@ -23,6 +28,8 @@
 // contiguous bytes (32 keys) with 256-bit loads one query block ahead.
 // Causally skipped tiles of dbias are written as zeros by this kernel, so dbias
 // needs no prior fill.
+// Rule kept by every barrier here: the next completion of a barrier needs progress of
+// every thread that waits on it, so a parity wait can never be two phases behind.
 //
 // Replaces _attn_bwd_dkdv / _attn_bwd_dkdv_inner of the reference
 // (flash_attention.py 237-454): same P, dS, dbias = dS, dK scaled by sm_scale.
@@ -32,7 +39,7 @@
 namespace fa {
 #ifdef FA_TRACE
 __device__ long long g_fa_trace_dkdv[8192];
-#define TR(role, step, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 16) g_fa_trace_dkdv[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
+#define TR(role, step, slot) do { if (blockIdx.x == 0 && (step) < 16) g_fa_trace_dkdv[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TR(role, step, slot) do {} while (0)
 #endif
@@ -54,6 +61,7 @@ struct DkdvParams {
   int64_t bias_sB, bias_sH, bias_sM;
   int64_t dk_sB, dk_sN, dk_sH, dv_sB, dv_sN, dv_sH;
   int H, M, N, D;
+  int n_nblk, n_tiles;  // key blocks per (batch, head); tiles = n_nblk * B * H
   int causal, write_dbias, bias_vec32, bias_b_mul, bias_h_mul;
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
@@ -61,7 +69,7 @@ struct DkdvParams {
 
 enum DkdvSite { kSiteKV = 1, kSiteQFull, kSiteQEmpty, kSiteDoFull, kSiteDoEmpty, kSiteSFull,
                 kSiteDpFull, kSitePReady, kSiteDsReady, kSiteDvDone, kSiteDkDone, kSiteStDone,
-                kSiteZeroReady, kSiteEpilogue, kSiteSFree, kSiteDpFree };
+                kSiteZeroReady, kSiteEpilogue, kSiteSFree, kSiteDpFree, kSiteKVEmpty };
 
 template <int DP>
 struct DkdvSmem {
@@ -86,11 +94,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   constexpr int kDoStages = L::kDoStages;
   constexpr uint32_t kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
   constexpr uint32_t kTmemCols = 512;
+  // BIAS: 0 none; 1 16-bit bias with 32-byte aligned rows and N % 32 == 0 (every thread's 32
+  // keys are whole sectors: paired-lane 256-bit loads); 2 byte mask; 3 16-bit bias, any layout
+  constexpr int BK = BIAS == 3 ? 1 : BIAS;  // element kind for the register helpers
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t kv_full, q_full[2], q_empty[2], do_full[2], do_empty[2];
+  __shared__ uint64_t kv_full, kv_empty, q_full[2], q_empty[2], do_full[2], do_empty[2];
   __shared__ uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done, st_done, zero_ready;
   __shared__ uint64_t s_free, dp_free;
   __shared__ uint32_t tmem_slot;
@@ -99,20 +110,31 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int nb = blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / p.H;
-  const int h = bh - b * p.H;
-  const int n0 = nb * 128;
   const int n_mblk = (p.M + 127) >> 7;
-  const int i_start = p.causal ? min(nb, n_mblk) : 0;
-  const int T_steps = n_mblk - i_start;
+
+  // Schedule: tiles are numbered (batch*head)-major; CTA c takes units c, c+G, c+2G, ... so
+  // that CTAs running at the same time work on neighbouring tiles and share Q / dO in L2.  A
+  // unit is one tile, or - causal - two consecutive entries of the per-(batch, head) order
+  // [first, last, first+1, last-1, ...]: a heavy and a light key block.
+  const int sched_sh = p.causal ? 1 : 0;
+  auto tile_at = [&](int it, int& bh, int& nb, int& i_start, int& T_steps) -> bool {
+    const int u = static_cast<int>(blockIdx.x) + (it >> sched_sh) * static_cast<int>(gridDim.x);
+    const int k = (u << sched_sh) + (it & sched_sh);
+    if (k >= p.n_tiles) return false;
+    bh = k / p.n_nblk;
+    const int pos = k - bh * p.n_nblk;
+    nb = p.causal ? ((pos & 1) ? p.n_nblk - 1 - (pos >> 1) : (pos >> 1)) : pos;
+    i_start = p.causal ? min(nb, n_mblk) : 0;
+    T_steps = n_mblk - i_start;
+    return true;
+  };
 
   WaitCtx ctx{&abort_flag, p.status, 2};
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&kv_full, 1);
+    mbar_init(&kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 2);
@@ -143,54 +165,78 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && live && T_steps > 0) {
+    if (lane == 0 && live) {
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
       tma_prefetch_desc(&p.map_do);
-      mbar_expect_tx(&kv_full, 2 * L::kTile);
-      for (int kb = 0; kb < KB; ++kb) {
-        tma_load_4d(smem + L::kK + kb * kBlk, &p.map_k, &kv_full, kb * 64, h, n0, b);
-        tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
-      }
       bool ok = true;
       constexpr int kBiasAhead = 2;  // bias tiles are pulled into L2 this many steps early
-      if (BIAS != 0) {
-        for (int t = 0; t < kBiasAhead && t < T_steps; ++t) {
-          const int mp = (i_start + t) * 128;
-          tma_prefetch_l2_4d(&p.map_bias, n0, mp, h * p.bias_h_mul, b * p.bias_b_mul);
-          if (BIAS == 1 && n0 + 64 < p.N)
-            tma_prefetch_l2_4d(&p.map_bias, n0 + 64, mp, h * p.bias_h_mul, b * p.bias_b_mul);
-        }
-      }
-      for (int t = 0; t < T_steps && ok; ++t) {
-        const int m0 = (i_start + t) * 128;
-        const int qs = t & 1;
-        if (BIAS != 0 && t + kBiasAhead < T_steps) {
-          const int mp = (i_start + t + kBiasAhead) * 128;
-          tma_prefetch_l2_4d(&p.map_bias, n0, mp, h * p.bias_h_mul, b * p.bias_b_mul);
-          if (BIAS == 1 && n0 + 64 < p.N)
-            tma_prefetch_l2_4d(&p.map_bias, n0 + 64, mp, h * p.bias_h_mul, b * p.bias_b_mul);
-        }
-        if (t >= 2) ok = mbar_wait(&q_empty[qs], ((t >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
+      uint32_t g = 0;                // steps issued so far, over all tiles
+      uint32_t kvi = 0;              // tiles with at least one step so far
+      int pf_done = 0;               // bias tiles of the coming tile already requested
+      int bh, nb, i_start, T_steps;
+      for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+        if (T_steps <= 0) continue;
+        const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
+        // K and V are single tiles: free once the previous tile's last S and dP are through
+        if (kvi >= 1) ok = mbar_wait(&kv_empty, (kvi - 1) & 1, ctx, kSiteKVEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&q_full[qs], L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kQ + qs * L::kTile + kb * kBlk, &p.map_q, &q_full[qs], kb * 64, h,
-                      m0, b);
-        const int ds = t % kDoStages;
-        const int du = t / kDoStages;
-        if (du >= 1) ok = mbar_wait(&do_empty[ds], (du - 1) & 1, ctx, kSiteDoEmpty, t);
-        if (!ok) break;
-        mbar_expect_tx(&do_full[ds], L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kDo + ds * L::kTile + kb * kBlk, &p.map_do, &do_full[ds], kb * 64,
-                      h, m0, b);
+        ++kvi;
+        mbar_expect_tx(&kv_full, 2 * L::kTile);
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_4d(smem + L::kK + kb * kBlk, &p.map_k, &kv_full, kb * 64, h, n0, b);
+          tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
+        }
+        // Bias tiles are pulled into L2 kBiasAhead steps before the row threads read them,
+        // as one stream over tile boundaries: the last steps of a tile request the first
+        // tiles of the next one (pf_done of them are out when that tile starts).
+        auto bias_l2 = [&](int b_, int h_, int n0_, int mblk) {
+          const int mp = mblk * 128;
+          tma_prefetch_l2_4d(&p.map_bias, n0_, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
+          if (BK == 1 && n0_ + 64 < p.N)
+            tma_prefetch_l2_4d(&p.map_bias, n0_ + 64, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
+        };
+        if (BIAS != 0) {
+          for (int t = pf_done; t < kBiasAhead && t < T_steps; ++t) bias_l2(b, h, n0, i_start + t);
+          pf_done = 0;
+        }
+        int bh2 = 0, nb2 = 0, is2 = 0, T2 = 0;
+        if (BIAS != 0 && !tile_at(it + 1, bh2, nb2, is2, T2)) T2 = 0;
+        for (int t = 0; t < T_steps && ok; ++t) {
+          const uint32_t gs = g + t;
+          const int m0 = (i_start + t) * 128;
+          const int qs = gs & 1;
+          if (BIAS != 0) {
+            if (t + kBiasAhead < T_steps) {
+              bias_l2(b, h, n0, i_start + t + kBiasAhead);
+            } else if (t + kBiasAhead - T_steps < T2) {
+              const int b2 = bh2 / p.H;
+              bias_l2(b2, bh2 - b2 * p.H, nb2 * 128, is2 + t + kBiasAhead - T_steps);
+              ++pf_done;
+            }
+          }
+          if (gs >= 2) ok = mbar_wait(&q_empty[qs], ((gs >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
+          if (!ok) break;
+          mbar_expect_tx(&q_full[qs], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kQ + qs * L::kTile + kb * kBlk, &p.map_q, &q_full[qs], kb * 64, h,
+                        m0, b);
+          const int ds = gs % kDoStages;
+          const uint32_t du = gs / kDoStages;
+          if (du >= 1) ok = mbar_wait(&do_empty[ds], (du - 1) & 1, ctx, kSiteDoEmpty, t);
+          if (!ok) break;
+          mbar_expect_tx(&do_full[ds], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kDo + ds * L::kTile + kb * kBlk, &p.map_do, &do_full[ds], kb * 64,
+                        h, m0, b);
+        }
+        g += T_steps;
       }
     }
   } else if (warp == 17) {
     // ------------------------------------------------------- MMA issuer: S and dP
-    if (lane == 0 && live && T_steps > 0) {
+    if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
       const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
@@ -199,50 +245,45 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const uint64_t q_km_0 = make_sdesc(q_addr, 0, 1024), q_km_1 = make_sdesc(q_addr + L::kTile, 0, 1024);
       const uint64_t do_km_0 = make_sdesc(do_addr, 0, 1024),
                      do_km_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, 0, 1024);
-      auto issue_s = [&](int t) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColS, (t & 1) ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
-                                          idesc_s, false);
-        mma_commit(&s_full);
-        mma_commit(&q_empty[t & 1]);
-      };
-      auto issue_dp = [&](int t) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, (t % kDoStages) ? do_km_1 : do_km_0, v_km,
-                                          kBlk, kBlk, idesc_s, false);
-        mma_commit(&dp_full);
-        mma_commit(&do_empty[t % kDoStages]);
-      };
-      bool ok = mbar_wait(&kv_full, 0, ctx, kSiteKV, 0);
-      if (ok) ok = mbar_wait(&q_full[0], 0, ctx, kSiteQFull, 0);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        ok = mbar_wait(&do_full[0], 0, ctx, kSiteDoFull, 0);
-      }
-      if (ok) {
-        tc_fence_after();
-        issue_dp(0);
-      }
-      for (int t = 0; t + 1 < T_steps && ok; ++t) {
-        const int ds1 = (t + 1) % kDoStages;
-        const uint32_t q_par = ((t + 1) >> 1) & 1, do_par = ((t + 1) / kDoStages) & 1;
-        // S_{t+1}: its columns are free once the row threads hold S_t in registers
-        const uint32_t pq = mbar_poll(&q_full[(t + 1) & 1], q_par);
-        ok = mbar_wait(&s_free, t & 1, ctx, kSiteSFree, t);
-        if (ok) ok = wait_polled(pq, &q_full[(t + 1) & 1], q_par, ctx, kSiteQFull, t + 1);
-        if (!ok) break;
-        TR(1, t, 1);
-        tc_fence_after();
-        const uint32_t pdo = mbar_poll(&do_full[ds1], do_par);
-        issue_s(t + 1);
-        TR(1, t, 2);
-        // dP_{t+1}: same for the dP columns; dO_{t+1} replaces dO_t after dV_t when single-staged
-        ok = mbar_wait(&dp_free, t & 1, ctx, kSiteDpFree, t);
-        if (ok) ok = wait_polled(pdo, &do_full[ds1], do_par, ctx, kSiteDoFull, t + 1);
-        if (!ok) break;
-        TR(1, t, 3);
-        tc_fence_after();
-        issue_dp(t + 1);
-        TR(1, t, 4);
+      bool ok = true;
+      uint32_t g = 0, kvi = 0;
+      int bh, nb, i_start, T_steps;
+      for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+        if (T_steps <= 0) continue;
+        ok = mbar_wait(&kv_full, kvi & 1, ctx, kSiteKV, it);
+        ++kvi;
+        for (int t = 0; t < T_steps && ok; ++t) {
+          const uint32_t gs = g + t;
+          const int qs = gs & 1, ds = gs % kDoStages;
+          const uint32_t q_par = (gs >> 1) & 1, do_par = (gs / kDoStages) & 1;
+          // S_gs: its columns are free once the row threads hold S_{gs-1} in registers
+          const uint32_t pq = mbar_poll(&q_full[qs], q_par);
+          if (gs >= 1) ok = mbar_wait(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
+          if (ok) ok = wait_polled(pq, &q_full[qs], q_par, ctx, kSiteQFull, t);
+          if (!ok) break;
+          TR(1, gs, 1);
+          tc_fence_after();
+          const uint32_t pdo = mbar_poll(&do_full[ds], do_par);
+          issue_gemm_ss<KS_D, false, false>(tmem + kColS, qs ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
+                                            idesc_s, false);
+          mma_commit(&s_full);
+          mma_commit(&q_empty[qs]);
+          TR(1, gs, 2);
+          // dP_gs: same for the dP columns; dO_gs replaces dO_{gs-1} after dV_{gs-1} when
+          // single-staged
+          if (gs >= 1) ok = mbar_wait(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
+          if (ok) ok = wait_polled(pdo, &do_full[ds], do_par, ctx, kSiteDoFull, t);
+          if (!ok) break;
+          TR(1, gs, 3);
+          tc_fence_after();
+          issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ds ? do_km_1 : do_km_0, v_km, kBlk, kBlk,
+                                            idesc_s, false);
+          mma_commit(&dp_full);
+          mma_commit(&do_empty[ds]);
+          if (t == T_steps - 1) mma_commit(&kv_empty);  // K and V may be replaced
+          TR(1, gs, 4);
+        }
+        g += T_steps;
       }
     }
     __syncwarp();
@@ -258,65 +299,79 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
                      do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
       const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
       bool ok = true;
-      for (int t = 0; t < T_steps && ok; ++t) {
-        const int qs = t & 1;
-        const int ds = t % kDoStages;
-        // dV += P^T dO  (dO_t must have landed: P_t only depends on S_t)
-        const uint32_t pdo = mbar_poll(&do_full[ds], (t / kDoStages) & 1);
-        const uint32_t pq = mbar_poll(&q_full[qs], (t >> 1) & 1);
-        ok = mbar_wait(&p_ready, t & 1, ctx, kSitePReady, t);
-        if (ok) ok = wait_polled(pdo, &do_full[ds], (t / kDoStages) & 1, ctx, kSiteDoFull, t);
-        if (!ok) break;
-        TR(2, t, 1);
-        tc_fence_after();
-        issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
-                                     t > 0);
-        mma_commit(&do_empty[ds]);
-        mma_commit(&dv_done);
-        TR(2, t, 2);
-        // dK += dS^T Q
-        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
-        if (ok) ok = wait_polled(pq, &q_full[qs], (t >> 1) & 1, ctx, kSiteQFull, t);
-        if (!ok) break;
-        TR(2, t, 3);
-        tc_fence_after();
-        issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
-                                     t > 0);
-        mma_commit(&q_empty[qs]);
-        mma_commit(&dk_done);
-        TR(2, t, 4);
+      uint32_t g = 0;
+      int bh, nb, i_start, T_steps;
+      for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+        for (int t = 0; t < T_steps && ok; ++t) {
+          const uint32_t gs = g + t;
+          const int qs = gs & 1;
+          const int ds = gs % kDoStages;
+          // dV += P^T dO  (dO must have landed: P only depends on S).  The first product of a
+          // tile overwrites dV / dK: P and dS of a new tile are only announced by all sixteen
+          // row warps after they have read the previous tile's accumulators.
+          const uint32_t pdo = mbar_poll(&do_full[ds], (gs / kDoStages) & 1);
+          const uint32_t pq = mbar_poll(&q_full[qs], (gs >> 1) & 1);
+          ok = mbar_wait(&p_ready, gs & 1, ctx, kSitePReady, t);
+          if (ok) ok = wait_polled(pdo, &do_full[ds], (gs / kDoStages) & 1, ctx, kSiteDoFull, t);
+          if (!ok) break;
+          TR(2, gs, 1);
+          tc_fence_after();
+          issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
+                                       t > 0);
+          mma_commit(&do_empty[ds]);
+          mma_commit(&dv_done);
+          TR(2, gs, 2);
+          // dK += dS^T Q
+          ok = mbar_wait(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
+          if (ok) ok = wait_polled(pq, &q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
+          if (!ok) break;
+          TR(2, gs, 3);
+          tc_fence_after();
+          issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
+                                       t > 0);
+          mma_commit(&q_empty[qs]);
+          mma_commit(&dk_done);
+          TR(2, gs, 4);
+        }
+        g += T_steps;
       }
     }
     __syncwarp();
   } else if (warp == 19) {
     // ------------------------------------------------------------- dbias stores
-    // phase 0 of st_done: zero tiles above the diagonal are out (or nothing to do);
-    // phase t+1: the store of dS_t has finished reading sDS.
+    // st_done completes once per step when the store of dS has finished reading sDS and -
+    // causal only - once per tile before that, when the zero tiles above the diagonal are out.
+    // (Without the zero tiles there is no per-tile completion: two completions in a row that
+    // no row thread has to wait for in between would let a parity wait fall two phases behind.)
     if (lane == 0 && live && p.write_dbias) {
       bool ok = true;
-      if (p.causal) {
-        ok = mbar_wait(&zero_ready, 0, ctx, kSiteZeroReady, 0);
-        if (ok) {
-          const int nz = min(nb, n_mblk);
-          for (int i = 0; i < nz; ++i) {
+      uint32_t g = 0;
+      int bh, nb, i_start, T_steps;
+      for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+        const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
+        if (p.causal) {
+          ok = mbar_wait(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
+          if (!ok) break;
+          for (int i = 0; i < i_start; ++i) {
             tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
             if (n0 + 64 < p.N)
               tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
           }
           tma_store_commit();
           tma_store_wait_read<0>();
+          mbar_arrive(&st_done);
         }
-      }
-      mbar_arrive(&st_done);
-      for (int t = 0; t < T_steps && ok; ++t) {
-        ok = mbar_wait(&ds_ready, t & 1, ctx, kSiteDsReady, t);
-        if (!ok) break;
-        const int m0 = (i_start + t) * 128;
-        tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
-        if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
-        tma_store_commit();
-        tma_store_wait_read<0>();
-        mbar_arrive(&st_done);
+        for (int t = 0; t < T_steps && ok; ++t) {
+          ok = mbar_wait(&ds_ready, (g + t) & 1, ctx, kSiteDsReady, t);
+          if (!ok) break;
+          const int m0 = (i_start + t) * 128;
+          tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
+          if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(&st_done);
+        }
+        g += T_steps;
       }
       tma_store_wait_all<0>();
     }
@@ -327,199 +382,227 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     const int qt = warp >> 2;              // column quarter: keys n0 + 32*qt .. +31
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     bool ok = live;
-    // this thread's four 16-byte chunks inside the [128][128] 16-bit tiles
-    uint8_t* sP = smem + L::kP + (qt >> 1) * kBlk;
-    uint8_t* sDS = smem + L::kDs + (qt >> 1) * kBlk;
-    const int chunk0 = (qt & 1) * 4;
+    // this thread's four 16-byte chunks inside the [128][128] 16-bit tiles: chunk c of the
+    // row lands at sp_row + ((chunk0 + c) ^ (r & 7)) * 16; the dS tile sits kDs - kP further
+    const uint32_t sp_row = smem_u32(smem + L::kP + (qt >> 1) * kBlk) + static_cast<uint32_t>(r) * 128u;
+    const uint32_t chunk0 = (qt & 1) * 4;
+    // tensor-memory address of this thread's 32 columns of S (dP: + kColDp)
+    const uint32_t tm_sc = tmem_addr(tmem, lane_base, kColS + qt * 32);
 
-    if (p.write_dbias && p.causal && ok) {
-      // zero tile for the causally skipped part of dbias
-      uint4* z = reinterpret_cast<uint4*>(smem + L::kDs);
-      for (int i = tid; i < 2 * kBlk / 16; i += 512) z[i] = make_uint4(0, 0, 0, 0);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&zero_ready);
-    }
-
-    const int col0 = n0 + qt * 32;
-    const int64_t bias_bh = b * p.bias_sB + h * p.bias_sH;
-    BiasRegs<BIAS> bnext;
-    float lse_next = INFINITY, delta_next = 0.f;
-    auto prefetch = [&](int t) {
-      const int m = (i_start + t) * 128 + r;
+    BiasRegs<BK> bnext;
+    float lse_next = -INFINITY, delta_next = 0.f;  // -LSE2 and delta of the coming step
+    // fetches bias / -LSE2 / delta of query block `mblk` for the tile (bh_, key column c0)
+    auto prefetch = [&](int bh_, int c0, int mblk) {
+      const int b_ = bh_ / p.H, h_ = bh_ - b_ * p.H;
+      const int64_t bias_bh = b_ * p.bias_sB + h_ * p.bias_sH;
+      const int m = mblk * 128 + r;
       const bool row_ok = m < p.M;
-      if (BIAS == 1 && p.bias_vec32 && col0 + 32 <= p.N) {
-        // warp-wide: one request per line, then a shuffle pass (see load_bias_rows_paired)
-        const int mrow0 = (i_start + t) * 128 + (warp & 3) * 32;
-        if constexpr (BIAS == 1)
-          load_bias_rows_paired(bnext, p.bias, bias_bh + (int64_t)mrow0 * p.bias_sM, p.bias_sM,
-                                p.M - mrow0, col0, lane);
-      } else if (BIAS != 0) {
-        load_bias_row<BIAS>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, col0, p.N,
-                            p.bias_vec32 != 0);
-      }
-      // clamped address: the value of a row beyond M is replaced when it is used
-      const int mc = row_ok ? m : p.M - 1;
-      lse_next = __ldg(p.lse + (int64_t)bh * p.M + mc);
-      delta_next = __ldg(p.delta + (int64_t)bh * p.M + mc);
-    };
-    if (ok && T_steps > 0) prefetch(0);
-
-    for (int t = 0; t < T_steps && ok; ++t) {
-      const int m0 = (i_start + t) * 128;
-      BiasRegs<BIAS> bcur = bnext;
       if constexpr (BIAS == 1) {
-        if (p.bias_vec32 && col0 + 32 <= p.N) redistribute_bias_rows(bcur, lane);
+        // warp-wide: one request per line, then a shuffle pass (see load_bias_rows_paired)
+        const int mrow0 = mblk * 128 + (warp & 3) * 32;
+        load_bias_rows_paired(bnext, p.bias, bias_bh + (int64_t)mrow0 * p.bias_sM, p.bias_sM,
+                              p.M - mrow0, c0, lane);
+      } else if constexpr (BIAS != 0) {
+        load_bias_row<BK>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, c0, p.N,
+                          p.bias_vec32 != 0);
       }
-      const bool row_in = m0 + r < p.M;
-      const float lse_raw = lse_next, delta_raw = delta_next;
-      if (t + 1 < T_steps) prefetch(t + 1);
-      // S_t and "dV_{t-1} has read P_{t-1}" are usually true by now: one combined look
-      uint32_t ps = 0, pdv = 1;
-      if (t >= 1)
-        mbar_poll2(&s_full, t & 1, &dv_done, (t - 1) & 1, ps, pdv);
-      else
-        ps = mbar_poll(&s_full, t & 1);
-
-      // ---- P
-      if (tid == 0) TR(0, t, 0);
-      ok = wait_warp_polled(ps, &s_full, t & 1, ctx, kSiteSFull, t);
-      if (!ok) break;
-      if (tid == 0) TR(0, t, 1);
-      tc_fence_after();
-      float pr[32];
-      tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
-      tmem_ld_wait();
-      // S_t now lives in registers: hand its columns back for S_{t+1}
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free);
-      // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
-      const float neg_lse = row_in ? -lse_raw : -INFINITY;
-      const float delta_r = row_in ? delta_raw : 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (BIAS == 1) {
-          const float2 f = P2::unpack(bcur.w[i >> 1]);
-          pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
-        } else if (BIAS == 2) {
-          const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
-          pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
-        } else {
-          pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
-        }
-      }
-      if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
-        int limit = p.N - col0;
-        if (p.causal) limit = min(limit, m0 + r - col0 + 1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= limit) pr[i] = 0.f;
-      }
-      if (tid == 0) TR(0, t, 2);
-      if (t >= 1) {
-        ok = wait_warp_polled(pdv, &dv_done, (t - 1) & 1, ctx, kSiteDvDone, t);
+      // -LSE2 / delta of the row; rows beyond M get -inf / 0, which makes their P and dS zero
+      lse_next = row_ok ? -__ldg(p.lse + (int64_t)bh_ * p.M + m) : -INFINITY;
+      delta_next = row_ok ? __ldg(p.delta + (int64_t)bh_ * p.M + m) : 0.f;
+    };
+    // Loop state is kept small on purpose (registers): the running step count gs, the tile
+    // counter it, and per tile bh, col0 and the current query block mb; the first query block
+    // of a tile is recomputed from col0 where needed.
+    uint32_t gs = 0;  // steps done so far, over all tiles
+    int bh, nb, i_start, T_steps;
+    if (ok && tile_at(0, bh, nb, i_start, T_steps) && T_steps > 0) prefetch(bh, nb * 128 + qt * 32, i_start);
+#pragma unroll 1
+    for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+      const int col0 = nb * 128 + qt * 32;
+      if (p.write_dbias && p.causal) {
+        // sDS becomes the zero tile for the causally skipped part of dbias: the last dbias
+        // store of the previous tile must have read it (the last dK product has: its barrier
+        // was seen in that tile's epilogue).  Causal completions of st_done: tile `it` owns
+        // indices gs+it (zero tiles out) and gs+it+1+t (store of step t).
+        if (it >= 1) ok = wait_warp(&st_done, (gs + it - 1) & 1, ctx, kSiteStDone, it);
         if (!ok) break;
+        const uint32_t z = sp_row - static_cast<uint32_t>(r) * 128u - (qt >> 1) * kBlk + (L::kDs - L::kP);
+        for (int i = tid; i < 2 * kBlk / 16; i += 512) sts128(z + i * 16, 0, 0, 0, 0);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&zero_ready);
       }
-      if (tid == 0) TR(0, t, 3);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 v;
-        v.x = P2::pack(pr[c * 8 + 0], pr[c * 8 + 1]);
-        v.y = P2::pack(pr[c * 8 + 2], pr[c * 8 + 3]);
-        v.z = P2::pack(pr[c * 8 + 4], pr[c * 8 + 5]);
-        v.w = P2::pack(pr[c * 8 + 6], pr[c * 8 + 7]);
-        *reinterpret_cast<uint4*>(sP + swz_off(r, chunk0 + c)) = v;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready);
-      if (tid == 0) TR(0, t, 4);
 
-      // ---- dS
-      // dP_t, "dK_{t-1} has read dS_{t-1}" and "its dbias store has": one combined look
-      uint32_t pdp = 0, pdk = 1, pst = 1;
-      if (t >= 1 && p.write_dbias)
-        mbar_poll3(&dp_full, t & 1, &dk_done, (t - 1) & 1, &st_done, t & 1, pdp, pdk, pst);
-      else if (t >= 1)
-        mbar_poll2(&dp_full, t & 1, &dk_done, (t - 1) & 1, pdp, pdk);
-      else if (p.write_dbias)
-        mbar_poll2(&dp_full, t & 1, &st_done, t & 1, pdp, pst);
-      else
-        pdp = mbar_poll(&dp_full, t & 1);
-      ok = wait_warp_polled(pdp, &dp_full, t & 1, ctx, kSiteDpFull, t);
-      if (!ok) break;
-      if (tid == 0) TR(0, t, 5);
-      tc_fence_after();
-      uint32_t dsu[16];
-      {
-        uint32_t dp[32];
-        tmem_ld32(tmem_addr(tmem, lane_base, kColDp + qt * 32), dp);
+#pragma unroll 1
+      for (int mb = i_start; mb < n_mblk && ok; ++mb, ++gs) {
+        const int i0 = p.causal ? min(col0 >> 7, n_mblk) : 0;  // first query block of the tile
+        const int t = mb - i0;
+        const int m0 = mb * 128;
+        BiasRegs<BK> bcur = bnext;
+        if constexpr (BIAS == 1) redistribute_bias_rows(bcur, lane);
+        const float neg_lse = lse_next, delta_r = delta_next;
+        if (mb + 1 < n_mblk) prefetch(bh, col0, mb + 1);
+        // S and "dV of the previous step has read P" are usually true by now: one combined look
+        uint32_t ps = 0, pdv = 1;
+        if (t >= 1)
+          mbar_poll2(&s_full, gs & 1, &dv_done, (gs - 1) & 1, ps, pdv);
+        else
+          ps = mbar_poll(&s_full, gs & 1);
+
+        // ---- P
+        if (tid == 0) TR(0, gs, 0);
+        ok = wait_warp_polled(ps, &s_full, gs & 1, ctx, kSiteSFull, t);
+        if (!ok) break;
+        if (tid == 0) TR(0, gs, 1);
+        tc_fence_after();
+        float pr[32];
+        tmem_ld32(tm_sc, reinterpret_cast<uint32_t*>(pr));
         tmem_ld_wait();
+        // S now lives in registers: hand its columns back for the next S
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&dp_free);
+        if (lane == 0) mbar_arrive(&s_free);
+        // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float d0 = pr[2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
-          const float d1 = pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
-          dsu[i] = P2::pack(d0, d1);
-        }
-      }
-      if (tid == 0) TR(0, t, 6);
-      if (t >= 1) {
-        ok = wait_warp_polled(pdk, &dk_done, (t - 1) & 1, ctx, kSiteDkDone, t);
-        if (!ok) break;
-      }
-      if (tid == 0) TR(0, t, 7);
-      if (p.write_dbias) {
-        ok = wait_warp_polled(pst, &st_done, t & 1, ctx, kSiteStDone, t);
-        if (!ok) break;
-      }
-      if (tid == 0) TR(0, t, 8);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + swz_off(r, chunk0 + c)) = v;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_ready);
-      if (tid == 0) TR(0, t, 9);
-    }
-
-    // ---- epilogue: dV, dK (rows = keys) -> global
-    if (ok && T_steps > 0) {
-      ok = wait_warp(&dv_done, (T_steps - 1) & 1, ctx, kSiteEpilogue, 0);
-      if (ok) ok = wait_warp(&dk_done, (T_steps - 1) & 1, ctx, kSiteEpilogue, 1);
-    }
-    if (ok) {
-      tc_fence_after();
-      const int n = n0 + r;
-      constexpr int kQD = DP / 4;  // columns of the head dim this thread stores (16 or 32)
-      const int d0 = qt * kQD;
-      T* dkrow = reinterpret_cast<T*>(p.dk) + b * p.dk_sB + (int64_t)n * p.dk_sN + h * p.dk_sH;
-      T* dvrow = reinterpret_cast<T*>(p.dv) + b * p.dv_sB + (int64_t)n * p.dv_sN + h * p.dv_sH;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        T* row = which == 0 ? dvrow : dkrow;
-        const uint32_t colbase = which == 0 ? kColDv : kColDk;
-        const float mul = which == 0 ? 1.0f : p.sm_scale;
-        uint32_t a[kQD];
-        if (T_steps > 0) {
-          tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, colbase + d0), a);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < kQD; ++i) a[i] = 0;
-        }
-        if (n < p.N) {
-#pragma unroll
-          for (int c = 0; c < kQD / 8; ++c) {
-            const int d = d0 + c * 8;
-            if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, mul);
+        for (int i = 0; i < 32; ++i) {
+          if (BK == 1) {
+            const float2 f = P2::unpack(bcur.w[i >> 1]);
+            pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
+          } else if (BK == 2) {
+            const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
+            pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
+          } else {
+            pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
           }
         }
+        if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
+          int limit = p.N - col0;
+          if (p.causal) limit = min(limit, m0 + r - col0 + 1);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i >= limit) pr[i] = 0.f;
+        }
+        if (tid == 0) TR(0, gs, 2);
+        if (t >= 1) {
+          ok = wait_warp_polled(pdv, &dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
+          if (!ok) break;
+        }
+        if (tid == 0) TR(0, gs, 3);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          sts128(sp_row + (((chunk0 + c) ^ (r & 7)) << 4), P2::pack(pr[c * 8 + 0], pr[c * 8 + 1]),
+                 P2::pack(pr[c * 8 + 2], pr[c * 8 + 3]), P2::pack(pr[c * 8 + 4], pr[c * 8 + 5]),
+                 P2::pack(pr[c * 8 + 6], pr[c * 8 + 7]));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready);
+        if (tid == 0) TR(0, gs, 4);
+
+        // ---- dS
+        // dP, "dK of the previous step has read dS" and "its dbias store has": one combined look
+        uint32_t pdp = 0, pdk = 1, pst = 1;
+        // sDS may be rewritten once its previous dbias store has read it: causal -> completion
+        // gs+it of st_done (see above); otherwise completion gs-1 (the store of step gs-1)
+        const uint32_t st_par = (p.causal ? gs + it : gs - 1) & 1;
+        const bool st_wait = p.write_dbias && (p.causal || gs >= 1);
+        if (t >= 1 && st_wait)
+          mbar_poll3(&dp_full, gs & 1, &dk_done, (gs - 1) & 1, &st_done, st_par, pdp, pdk, pst);
+        else if (t >= 1)
+          mbar_poll2(&dp_full, gs & 1, &dk_done, (gs - 1) & 1, pdp, pdk);
+        else if (st_wait)
+          mbar_poll2(&dp_full, gs & 1, &st_done, st_par, pdp, pst);
+        else
+          pdp = mbar_poll(&dp_full, gs & 1);
+        ok = wait_warp_polled(pdp, &dp_full, gs & 1, ctx, kSiteDpFull, t);
+        if (!ok) break;
+        if (tid == 0) TR(0, gs, 5);
+        tc_fence_after();
+        uint32_t dsu[16];
+        // dP is fetched in two halves: fewer registers are live at once
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t dp[16];
+          tmem_ld16(tm_sc + (kColDp - kColS) + hf * 16, dp);
+          tmem_ld_wait();
+          if (hf == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&dp_free);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int e = hf * 16 + 2 * i;
+            const float d0 = pr[e] * (__uint_as_float(dp[2 * i]) - delta_r);
+            const float d1 = pr[e + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
+            dsu[hf * 8 + i] = P2::pack(d0, d1);
+          }
+        }
+        if (tid == 0) TR(0, gs, 6);
+        if (t >= 1) {
+          ok = wait_warp_polled(pdk, &dk_done, (gs - 1) & 1, ctx, kSiteDkDone, t);
+          if (!ok) break;
+        }
+        if (tid == 0) TR(0, gs, 7);
+        if (st_wait) {
+          ok = wait_warp_polled(pst, &st_done, st_par, ctx, kSiteStDone, t);
+          if (!ok) break;
+        }
+        if (tid == 0) TR(0, gs, 8);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          sts128(sp_row + (L::kDs - L::kP) + (((chunk0 + c) ^ (r & 7)) << 4), dsu[c * 4 + 0],
+                 dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_ready);
+        if (tid == 0) TR(0, gs, 9);
+      }
+      if (!ok) break;
+
+      // the next tile's first bias / LSE / delta rows travel while this tile's result is stored
+      {
+        int bh2, nb2, is2, T2;
+        if (tile_at(it + 1, bh2, nb2, is2, T2) && T2 > 0) prefetch(bh2, nb2 * 128 + qt * 32, is2);
+      }
+
+      // ---- epilogue: dV, dK (rows = keys) -> global
+      const int steps_here = n_mblk - (p.causal ? min(col0 >> 7, n_mblk) : 0);
+      if (steps_here > 0) {
+        ok = wait_warp(&dv_done, (gs - 1) & 1, ctx, kSiteEpilogue, 0);
+        if (ok) ok = wait_warp(&dk_done, (gs - 1) & 1, ctx, kSiteEpilogue, 1);
+        if (!ok) break;
+      }
+      {
+        tc_fence_after();
+        const int b = bh / p.H, h = bh - b * p.H;
+        const int n = (col0 & ~127) + r;
+        constexpr int kQD = DP / 4;  // columns of the head dim this thread stores (16 or 32)
+        const int d0 = qt * kQD;
+        T* dkrow = reinterpret_cast<T*>(p.dk) + b * p.dk_sB + (int64_t)n * p.dk_sN + h * p.dk_sH;
+        T* dvrow = reinterpret_cast<T*>(p.dv) + b * p.dv_sB + (int64_t)n * p.dv_sN + h * p.dv_sH;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          T* row = which == 0 ? dvrow : dkrow;
+          const uint32_t colbase = which == 0 ? kColDv : kColDk;
+          const float mul = which == 0 ? 1.0f : p.sm_scale;
+          uint32_t a[kQD];
+          if (steps_here > 0) {
+            tmem_ld_cols<kQD>(tm_sc - qt * 32 + colbase + d0, a);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < kQD; ++i) a[i] = 0;
+          }
+          if (n < p.N) {
+#pragma unroll
+            for (int c = 0; c < kQD / 8; ++c) {
+              const int d = d0 + c * 8;
+              if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, mul);
+            }
+          }
+        }
+        // the accumulators are in registers: the next tile's first products may overwrite them
+        tc_fence_before();
       }
     }
   }
@@ -550,7 +633,9 @@ template <int DP, typename T>
 int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t stream) {
   switch (bias_kind) {
     case FA_BIAS_NONE: return launch_inst<DP, T, 0>(kp, grid, stream);
-    case FA_BIAS_SAME: return launch_inst<DP, T, 1>(kp, grid, stream);
+    case FA_BIAS_SAME:
+      return kp.bias_vec32 && kp.N % 32 == 0 ? launch_inst<DP, T, 1>(kp, grid, stream)
+                                             : launch_inst<DP, T, 3>(kp, grid, stream);
     case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(kp, grid, stream);
     default: return FA_ERR_UNSUPPORTED;
   }
@@ -634,7 +719,10 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   }
   kp.scale_log2 = p.sm_scale * kLog2e;
   kp.sm_scale = p.sm_scale;
-  const dim3 grid((p.N + 127) / 128, p.B * p.H);
+  kp.n_nblk = (p.N + 127) / 128;
+  kp.n_tiles = kp.n_nblk * p.B * p.H;
+  const int units = p.causal ? (kp.n_tiles + 1) / 2 : kp.n_tiles;
+  const dim3 grid(persistent_grid(units));
   const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {
     return dp == 64 ? launch_bias<64, __nv_bfloat16>(kp, p.bias_kind, grid, stream)
