@@ -11,8 +11,8 @@
 //   warp 16    TMA producer (one lane): K, V per tile; Q ring (2), dO ring; bias tiles
 //              are asked into L2 two steps ahead
 //   warp 17    MMA issuer for S and dP (one lane), tensor-memory owner
-//   warp 18    MMA issuer for dV and dK (one lane)
-//   warp 19    bulk tensor stores of the dS tile into dbias (one lane)
+//   warp 18    MMA issuer for dV and dK, bulk tensor stores of dS into dbias (one lane)
+//   warp 19    TMA loads of the 16-bit bias tiles (one lane)
 // A barrier operation answers after ~200 cycles on this GPU, so two issuers keep
 // the tensor pipe fed while the other one waits, and every role polls the
 // barriers it will need before it starts a stretch of independent work.
@@ -24,8 +24,11 @@
 //   dV += P^T dO_t          (sP and dO_t consumed MN-major)
 //   dK += dS^T Q_t          (sDS and Q_t consumed MN-major)
 //   dbias[b,h,m-block,n-block] <- sDS  (one bulk tensor store of the same tile)
-// The bias never touches shared memory: every row thread fetches its own 64
-// contiguous bytes (32 keys) with 256-bit loads one query block ahead.
+// A 16-bit bias tile is brought in by TMA (warp 19) and lands exactly where the row threads
+// then write P: each thread reads the four 16-byte chunks it is about to overwrite, so the
+// bias needs no shared memory of its own (none is left at head dim 128); warp 18 then also
+// issues the dbias stores.  A byte mask is read by the row threads straight from global
+// memory, 32 contiguous bytes per thread, one query block ahead.
 // Causally skipped tiles of dbias are written as zeros by this kernel, so dbias
 // needs no prior fill.
 // Rule kept by every barrier here: the next completion of a barrier needs progress of
@@ -69,7 +72,7 @@ struct DkdvParams {
 
 enum DkdvSite { kSiteKV = 1, kSiteQFull, kSiteQEmpty, kSiteDoFull, kSiteDoEmpty, kSiteSFull,
                 kSiteDpFull, kSitePReady, kSiteDsReady, kSiteDvDone, kSiteDkDone, kSiteStDone,
-                kSiteZeroReady, kSiteEpilogue, kSiteSFree, kSiteDpFree, kSiteKVEmpty };
+                kSiteZeroReady, kSiteEpilogue, kSiteSFree, kSiteDpFree, kSiteKVEmpty, kSiteBiasFull };
 
 template <int DP>
 struct DkdvSmem {
@@ -94,16 +97,16 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   constexpr int kDoStages = L::kDoStages;
   constexpr uint32_t kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
   constexpr uint32_t kTmemCols = 512;
-  // BIAS: 0 none; 1 16-bit bias with 32-byte aligned rows and N % 32 == 0 (every thread's 32
-  // keys are whole sectors: paired-lane 256-bit loads); 2 byte mask; 3 16-bit bias, any layout
-  constexpr int BK = BIAS == 3 ? 1 : BIAS;  // element kind for the register helpers
+  // BIAS: 0 none; 1 16-bit bias, brought in by TMA (warp 19; the dbias stores then move to
+  // warp 18); 2 byte mask, read by the row threads from global memory
+  constexpr int BK = BIAS;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t kv_full, kv_empty, q_full[2], q_empty[2], do_full[2], do_empty[2];
   __shared__ uint64_t s_full, dp_full, p_ready, ds_ready, dv_done, dk_done, st_done, zero_ready;
-  __shared__ uint64_t s_free, dp_free;
+  __shared__ uint64_t s_free, dp_free, bias_full;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -151,6 +154,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     mbar_init(&zero_ready, 16);
     mbar_init(&s_free, 16);
     mbar_init(&dp_free, 16);
+    mbar_init(&bias_full, 1);
     mbar_fence_init();
   }
   if (warp == 17) {
@@ -298,10 +302,31 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const uint64_t do_mn_0 = make_sdesc(do_addr, kBlk, 1024),
                      do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
       const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
+      // This thread also sends the dS tiles out as dbias (a bias gradient only exists for a
+      // 16-bit bias).  st_done completes once per step when the store of dS has finished
+      // reading sDS and - causal only - once per tile before that, when the zero tiles above
+      // the diagonal are out.  (Without the zero tiles there is no per-tile completion: two
+      // completions in a row that no row thread has to wait for in between would let a parity
+      // wait fall two phases behind.)  The wait for the store's read sits right after the
+      // store: the next thing this thread needs, P of the next step, is further away.
+      const bool stores_here = BIAS == 1 && p.write_dbias;
       bool ok = true;
       uint32_t g = 0;
       int bh, nb, i_start, T_steps;
       for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
+        const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
+        if (stores_here && p.causal) {
+          ok = mbar_wait(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
+          if (!ok) break;
+          for (int i = 0; i < i_start; ++i) {
+            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
+            if (n0 + 64 < p.N)
+              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
+          }
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(&st_done);
+        }
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
           const int qs = gs & 1;
@@ -332,48 +357,48 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           mma_commit(&q_empty[qs]);
           mma_commit(&dk_done);
           TR(2, gs, 4);
+          if (stores_here) {
+            const int m0 = (i_start + t) * 128;
+            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
+            if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+            mbar_arrive(&st_done);
+          }
         }
         g += T_steps;
       }
+      if (stores_here) tma_store_wait_all<0>();
     }
     __syncwarp();
   } else if (warp == 19) {
-    // ------------------------------------------------------------- dbias stores
-    // st_done completes once per step when the store of dS has finished reading sDS and -
-    // causal only - once per tile before that, when the zero tiles above the diagonal are out.
-    // (Without the zero tiles there is no per-tile completion: two completions in a row that
-    // no row thread has to wait for in between would let a parity wait fall two phases behind.)
-    if (lane == 0 && live && p.write_dbias) {
+    // ----------------------------------------------------------- bias tile loads
+    // The [128 rows][128 keys] 16-bit bias tile of a step lands exactly where the row threads
+    // will then write P (same two swizzled blocks, every thread reads the four 16-byte
+    // chunks it is about to overwrite): no extra shared memory.  sP is free for it once the
+    // dV product of the previous step has read P.
+    if (BIAS == 1 && lane == 0 && live) {
+      tma_prefetch_desc(&p.map_bias);
       bool ok = true;
       uint32_t g = 0;
       int bh, nb, i_start, T_steps;
       for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
         const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
-        if (p.causal) {
-          ok = mbar_wait(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
-          if (!ok) break;
-          for (int i = 0; i < i_start; ++i) {
-            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
-            if (n0 + 64 < p.N)
-              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
-          }
-          tma_store_commit();
-          tma_store_wait_read<0>();
-          mbar_arrive(&st_done);
-        }
+        const bool two = n0 + 64 < p.N;
         for (int t = 0; t < T_steps && ok; ++t) {
-          ok = mbar_wait(&ds_ready, (g + t) & 1, ctx, kSiteDsReady, t);
+          const uint32_t gs = g + t;
+          if (gs >= 1) ok = mbar_wait(&dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
           if (!ok) break;
           const int m0 = (i_start + t) * 128;
-          tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
-          if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
-          tma_store_commit();
-          tma_store_wait_read<0>();
-          mbar_arrive(&st_done);
+          mbar_expect_tx(&bias_full, two ? 2 * kBlk : kBlk);
+          tma_load_4d(smem + L::kP, &p.map_bias, &bias_full, n0, m0, h * p.bias_h_mul,
+                      b * p.bias_b_mul);
+          if (two)
+            tma_load_4d(smem + L::kP + kBlk, &p.map_bias, &bias_full, n0 + 64, m0, h * p.bias_h_mul,
+                        b * p.bias_b_mul);
         }
         g += T_steps;
       }
-      tma_store_wait_all<0>();
     }
     __syncwarp();
   } else {
@@ -389,7 +414,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     // tensor-memory address of this thread's 32 columns of S (dP: + kColDp)
     const uint32_t tm_sc = tmem_addr(tmem, lane_base, kColS + qt * 32);
 
-    BiasRegs<BK> bnext;
+    constexpr int BR = BIAS == 1 ? 0 : BK;  // bias staged in registers only for kinds 2 and 3
+    BiasRegs<BR> bnext;
     float lse_next = -INFINITY, delta_next = 0.f;  // -LSE2 and delta of the coming step
     // fetches bias / -LSE2 / delta of query block `mblk` for the tile (bh_, key column c0)
     auto prefetch = [&](int bh_, int c0, int mblk) {
@@ -397,12 +423,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const int64_t bias_bh = b_ * p.bias_sB + h_ * p.bias_sH;
       const int m = mblk * 128 + r;
       const bool row_ok = m < p.M;
-      if constexpr (BIAS == 1) {
-        // warp-wide: one request per line, then a shuffle pass (see load_bias_rows_paired)
-        const int mrow0 = mblk * 128 + (warp & 3) * 32;
-        load_bias_rows_paired(bnext, p.bias, bias_bh + (int64_t)mrow0 * p.bias_sM, p.bias_sM,
-                              p.M - mrow0, c0, lane);
-      } else if constexpr (BIAS != 0) {
+      if constexpr (BR != 0) {
         load_bias_row<BK>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, c0, p.N,
                           p.bias_vec32 != 0);
       }
@@ -438,13 +459,16 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         const int i0 = p.causal ? min(col0 >> 7, n_mblk) : 0;  // first query block of the tile
         const int t = mb - i0;
         const int m0 = mb * 128;
-        BiasRegs<BK> bcur = bnext;
-        if constexpr (BIAS == 1) redistribute_bias_rows(bcur, lane);
+        BiasRegs<BR> bcur = bnext;
         const float neg_lse = lse_next, delta_r = delta_next;
         if (mb + 1 < n_mblk) prefetch(bh, col0, mb + 1);
         // S and "dV of the previous step has read P" are usually true by now: one combined look
-        uint32_t ps = 0, pdv = 1;
-        if (t >= 1)
+        uint32_t ps = 0, pdv = 1, pb = 1;
+        if (BIAS == 1 && t >= 1)
+          mbar_poll3(&s_full, gs & 1, &dv_done, (gs - 1) & 1, &bias_full, gs & 1, ps, pdv, pb);
+        else if (BIAS == 1)
+          mbar_poll2(&s_full, gs & 1, &bias_full, gs & 1, ps, pb);
+        else if (t >= 1)
           mbar_poll2(&s_full, gs & 1, &dv_done, (gs - 1) & 1, ps, pdv);
         else
           ps = mbar_poll(&s_full, gs & 1);
@@ -463,6 +487,23 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free);
         // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
+        if constexpr (BIAS == 1) {
+          // the bias tile sits where this thread's P chunks go
+          ok = wait_warp_polled(pb, &bias_full, gs & 1, ctx, kSiteBiasFull, t);
+          if (!ok) break;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = lds128(sp_row + (((chunk0 + c) ^ (r & 7)) << 4));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = P2::unpack(w[e]);
+              const int i = c * 8 + e * 2;
+              pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf(f.x, kLog2e, neg_lse)));
+              pr[i + 1] = ex2(fmaf(pr[i + 1], p.scale_log2, fmaf(f.y, kLog2e, neg_lse)));
+            }
+          }
+        } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (BK == 1) {
@@ -474,6 +515,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           } else {
             pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
           }
+        }
         }
         if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
           int limit = p.N - col0;
@@ -633,9 +675,7 @@ template <int DP, typename T>
 int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t stream) {
   switch (bias_kind) {
     case FA_BIAS_NONE: return launch_inst<DP, T, 0>(kp, grid, stream);
-    case FA_BIAS_SAME:
-      return kp.bias_vec32 && kp.N % 32 == 0 ? launch_inst<DP, T, 1>(kp, grid, stream)
-                                             : launch_inst<DP, T, 3>(kp, grid, stream);
+    case FA_BIAS_SAME: return launch_inst<DP, T, 1>(kp, grid, stream);
     case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(kp, grid, stream);
     default: return FA_ERR_UNSUPPORTED;
   }

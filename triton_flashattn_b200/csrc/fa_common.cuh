@@ -538,6 +538,16 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, ui
                : "memory");
 }
 
+// 16-byte load from shared memory through a 32-bit shared-space address.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -637,49 +647,6 @@ __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bi
     }
     br.w[i] = word;
   }
-}
-
-// 16-bit bias for one warp: rows row0 .. row0+31 (lane = row), 32 columns from col0
-// (64 bytes per row).  Lanes 2k and 2k+1 fetch the two 32-byte sectors of row k in
-// the SAME instruction (rows 0-15, then rows 16-31), so the memory system sees one
-// request per 128-byte line instead of one per sector; a shuffle pass then hands
-// every lane the 64 bytes of its own row.  `row_off0` is the element offset of
-// (row0, 0), `rows_valid` the number of rows of this warp that exist.
-// Requires col0 + 32 <= N and 32-byte aligned rows (the caller checks).
-__device__ __forceinline__ void load_bias_rows_paired(BiasRegs<1>& br, const void* bias_base,
-                                                      int64_t row_off0, int64_t row_stride,
-                                                      int rows_valid, int col0, int lane) {
-  const uint8_t* base = reinterpret_cast<const uint8_t*>(bias_base);
-  uint32_t a[8], b[8];
-  const int rsel = lane >> 1, sec = lane & 1;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) a[i] = b[i] = 0;
-  if (rsel < rows_valid) ldg256(base + (row_off0 + rsel * row_stride + col0) * 2 + sec * 32, a);
-  if (rsel + 16 < rows_valid)
-    ldg256(base + (row_off0 + (rsel + 16) * row_stride + col0) * 2 + sec * 32, b);
-  // raw sectors; redistribute_bias_rows() turns them into this lane's own row later,
-  // once the loads have had a whole step to arrive
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    br.w[i] = a[i];
-    br.w[8 + i] = b[i];
-  }
-}
-__device__ __forceinline__ void redistribute_bias_rows(BiasRegs<1>& br, int lane) {
-  const int src = (lane & 15) * 2;
-  const bool low = lane < 16;
-  uint32_t out[16];
-#pragma unroll
-  for (int sct = 0; sct < 2; ++sct) {
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const uint32_t va = __shfl_sync(0xffffffffu, br.w[w], src + sct);
-      const uint32_t vb = __shfl_sync(0xffffffffu, br.w[8 + w], src + sct);
-      out[sct * 8 + w] = low ? va : vb;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) br.w[i] = out[i];
 }
 
 // Packs 8 consecutive fp32 values (scaled) into one 16-byte vector of T.
