@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       tma_prefetch_desc(&p.map_v);
       tma_prefetch_desc(&p.map_do);
       bool ok = true;
-      constexpr int kBiasAhead = 2;  // bias tiles are pulled into L2 this many steps early
+      constexpr int kBiasAhead = 1;  // bias tiles are pulled into L2 this many steps early
       uint32_t g = 0;                // steps issued so far, over all tiles
       uint32_t kvi = 0;              // tiles with at least one step so far
       int pf_done = 0;               // bias tiles of the coming tile already requested
