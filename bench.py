@@ -61,6 +61,11 @@ def load_peaks():
     return dict(hbm_gbs=6650.0, tflops=1400.0, tflops_burst=1590.0, source="fallback")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one dkdv_kernel launch of config 3 at B=2,
+# divided by 2 (ncu capture summarised in profiles/dkdv_kernel_config3_b2_ncu_full.md)
+DKDV_DRAM_BYTES_PER_BATCH_CONFIG3 = (340.93e6 + 260.09e6) / 2
+
+
 def flops(w, which):
     c = 0.5 if w["causal"] else 1.0
     mult = {"fwd": 4, "bwd": 10, "fwd+bwd": 14, "dkdv": 8, "dq_recompute": 6, "dq_from_ds": 2}[which]
@@ -364,6 +369,11 @@ def main():
                 roofline = {"kernel": "dkdv_kernel", "bound": "hbm", "achieved": kd["gbs"],
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kd["gbs"] / peaks["hbm_gbs"], 3),
                             "traffic": None, "peak_source": peaks["source"]}
+            # DRAM traffic of one dK/dV launch: from the ncu capture of this workload at B=2
+            # (profiles/dkdv_kernel_config3_b2_ncu_full.md: 340.9 MB read + 260.1 MB written);
+            # the kernel's traffic is proportional to B
+            if args.workload == "3" and not args.bias:
+                roofline["traffic"] = int(DKDV_DRAM_BYTES_PER_BATCH_CONFIG3 * w["B"])
             roofline["sum_roof_over_sum_measured"] = round(
                 sum(x["roof_ms"] for x in kernels.values()) / sum(x["ms"] for x in kernels.values()), 3)
             del o, lse, dq, dk, dv, dbias, delta
