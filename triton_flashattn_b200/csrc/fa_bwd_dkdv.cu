@@ -165,6 +165,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  grid_dep_launch_next();
+  grid_dep_wait();  // the previous kernel's results (and its status word) are visible from here
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
   if (warp == 16) {
@@ -667,8 +669,7 @@ int launch_inst(const DkdvParams& kp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 640, L::kDynamic, stream>>>(kp);
-  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+  return launch_overlapped(kern, grid, 640, L::kDynamic, stream, kp);
 }
 
 template <int DP, typename T>

@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  grid_dep_launch_next();
+  grid_dep_wait();  // the previous kernel's results (and its status word) are visible from here
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
   if (warp == 16) {
@@ -393,6 +395,8 @@ __global__ void __launch_bounds__(192, 2) dq_from_ds_kernel(const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  grid_dep_launch_next();
+  grid_dep_wait();  // the previous kernel's results (and its status word) are visible from here
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
   if (warp == 4) {
@@ -480,8 +484,7 @@ int launch_recompute(const DqParams& kp, dim3 grid, cudaStream_t stream) {
   static bool configured[64] = {};
   auto kern = dq_recompute_kernel<DP, T, BIAS>;
   if (int r = configure(kern, L::kDynamic, configured)) return r;
-  kern<<<grid, 608, L::kDynamic, stream>>>(kp);
-  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+  return launch_overlapped(kern, grid, 608, L::kDynamic, stream, kp);
 }
 
 template <int DP, typename T>
@@ -490,8 +493,7 @@ int launch_from_ds(const DqParams& kp, dim3 grid, cudaStream_t stream) {
   static bool configured[64] = {};
   auto kern = dq_from_ds_kernel<DP, T>;
   if (int r = configure(kern, L::kDynamic, configured)) return r;
-  kern<<<grid, 192, L::kDynamic, stream>>>(kp);
-  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+  return launch_overlapped(kern, grid, 192, L::kDynamic, stream, kp);
 }
 
 template <int DP, typename T>

@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const PreParams p) {
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh - b * p.H;
   float acc = 0.f;
+  grid_dep_launch_next();
+  grid_dep_wait();  // o and do of the previous kernels are visible from here
   if (m < p.M) {
     const T* orow = reinterpret_cast<const T*>(p.o) + b * p.o_sB + (int64_t)m * p.o_sM + h * p.o_sH;
     const T* drow =
@@ -67,10 +69,9 @@ int launch_bwd_pre(const fa_params& p, cudaStream_t stream, int* /*status*/) {
   const int rows_per_block = 256 / (p.D / 8);
   const dim3 grid((p.M + rows_per_block - 1) / rows_per_block, p.B * p.H);
   if (p.dtype == FA_BF16)
-    bwd_pre_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(pp);
+    return launch_overlapped(bwd_pre_kernel<__nv_bfloat16>, grid, 256, 0, stream, pp);
   else
-    bwd_pre_kernel<__half><<<grid, 256, 0, stream>>>(pp);
-  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+    return launch_overlapped(bwd_pre_kernel<__half>, grid, 256, 0, stream, pp);
 }
 
 }  // namespace fa

@@ -554,6 +554,16 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// Programmatic dependent launch.  Every kernel of this library is launched with the
+// "programmatic stream serialization" attribute: its CTAs may be placed on an SM as soon as
+// the previous kernel's CTA there has left, and run their prologue (barrier set-up, tensor
+// memory allocation).  grid_dep_wait() returns once the previous kernel has completed
+// and its memory is visible; nothing before it may touch global memory.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch_next() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads'.
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

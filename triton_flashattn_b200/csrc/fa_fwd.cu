@@ -149,6 +149,8 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   // A kernel launched after an earlier one recorded an error does no work.
+  grid_dep_launch_next();
+  grid_dep_wait();  // the previous kernel's results (and its status word) are visible from here
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
   if (warp == 16) {
@@ -520,8 +522,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  kern<<<grid, 640, L::kDynamic, stream>>>(fp);
-  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+  return launch_overlapped(kern, grid, 640, L::kDynamic, stream, fp);
 }
 
 template <int DP, typename T>

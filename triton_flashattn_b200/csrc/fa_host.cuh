@@ -38,6 +38,23 @@ int launch_selftest(int mode, int dtype, const void* a, const void* b, void* c, 
 // per CTA.
 int persistent_grid(int n_tiles);
 
+// Launch with the programmatic-stream-serialization attribute (see grid_dep_wait()).
+template <typename Kern, typename Params>
+inline int launch_overlapped(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream,
+                             const Params& params) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, params) == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+}
+
 // Head dims are computed on a padded width: 16/32/64 -> 64, 128 -> 128.
 inline int padded_head_dim(int d) { return d <= 64 ? 64 : d; }
 
