@@ -302,8 +302,7 @@ def main():
         step()
     barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.start()  # every rank watches its own GPU
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     start.record()
@@ -312,11 +311,17 @@ def main():
     end.record()
     barrier()
     ms = start.elapsed_time(end) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
+    ranks = None
     if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+        # per-rank time and clock, so that a slow rank can be told from a slow program
+        mine = torch.tensor([ms, clocks["sm_mhz"] or 0.0, float("sw_power_cap" in clocks["reasons"]),
+                             float(any(r != "sw_power_cap" for r in clocks["reasons"]))], device=device)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        ranks = [{"ms": round(x[0].item(), 4), "sm_mhz": x[1].item(), "sw_power_cap": bool(x[2].item()),
+                  "other_slowdown": bool(x[3].item())} for x in allr]
+        ms = max(r["ms"] for r in ranks)
     st = _cabi.device_status(local_rank)
     if st[0] != 0:
         raise RuntimeError(f"kernel abandoned a bounded wait: {st}")
@@ -441,7 +446,7 @@ def main():
             "config": {"workload": wname, "per_gpu": True, "l2": "inputs larger than L2 (no flush needed)"
                        if w["bias"] else "inputs smaller than L2, no flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps,
-            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "ranks": ranks,
             "frac_of_roofline_sum": roofline["sum_roof_over_sum_measured"] if roofline else None,
         }
         print(json.dumps(line), flush=True)
