@@ -501,21 +501,23 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
             for (int e = 0; e < 4; ++e) {
               const float2 f = P2::unpack(w[e]);
               const int i = c * 8 + e * 2;
-              pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf(f.x, kLog2e, neg_lse)));
-              pr[i + 1] = ex2(fmaf(pr[i + 1], p.scale_log2, fmaf(f.y, kLog2e, neg_lse)));
+              const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
+                                    ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
+              pr[i] = ex2(f2_lo(a));
+              pr[i + 1] = ex2(f2_hi(a));
             }
           }
         } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (BK == 1) {
-            const float2 f = P2::unpack(bcur.w[i >> 1]);
-            pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
-          } else if (BK == 2) {
-            const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
-            pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
+        for (int i = 0; i < 32; i += 2) {
+          const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+          if (BK == 2) {
+            const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
+            pr[i] = (m2 & 0xFFu) != 0 ? ex2(f2_lo(a)) : 0.f;
+            pr[i + 1] = (m2 & 0xFF00u) != 0 ? ex2(f2_hi(a)) : 0.f;
           } else {
-            pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
+            pr[i] = ex2(f2_lo(a));
+            pr[i + 1] = ex2(f2_hi(a));
           }
         }
         }
@@ -576,9 +578,10 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int e = hf * 16 + 2 * i;
-            const float d0 = pr[e] * (__uint_as_float(dp[2 * i]) - delta_r);
-            const float d1 = pr[e + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
-            dsu[hf * 8 + i] = P2::pack(d0, d1);
+            const f32x2 d = fmul2(f2(pr[e], pr[e + 1]),
+                                  fadd2(f2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1])),
+                                        f2(-delta_r, -delta_r)));
+            dsu[hf * 8 + i] = P2::pack(f2_lo(d), f2_hi(d));
           }
         }
         if (tid == 0) TR(0, gs, 6);

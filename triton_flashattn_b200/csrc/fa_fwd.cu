@@ -353,8 +353,10 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 f = P2::unpack(w[e]);
-              s[c * 8 + e * 2] = fmaf(s[c * 8 + e * 2], p.sm_scale, f.x);
-              s[c * 8 + e * 2 + 1] = fmaf(s[c * 8 + e * 2 + 1], p.sm_scale, f.y);
+              const int i = c * 8 + e * 2;
+              const f32x2 t = ffma2(f2(s[i], s[i + 1]), f2(p.sm_scale, p.sm_scale), f2(f.x, f.y));
+              s[i] = f2_lo(t);
+              s[i + 1] = f2_hi(t);
             }
           }
         } else {
@@ -439,22 +441,21 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       }
       if (tid == 0) TR(0, g, 7);
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      f32x2 sum01 = f2(0.f, 0.f), sum23 = f2(0.f, 0.f);
+      const f32x2 mul2 = f2(mul, mul), negm2 = f2(neg_m, neg_m);
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
-        const float p0 = ex2(fmaf(s[2 * i], mul, neg_m));
-        const float p1 = ex2(fmaf(s[2 * i + 1], mul, neg_m));
-        const float p2 = ex2(fmaf(s[2 * i + 2], mul, neg_m));
-        const float p3 = ex2(fmaf(s[2 * i + 3], mul, neg_m));
-        sum0 += p0;
-        sum1 += p1;
-        sum2 += p2;
-        sum3 += p3;
+        const f32x2 a01 = ffma2(f2(s[2 * i], s[2 * i + 1]), mul2, negm2);
+        const f32x2 a23 = ffma2(f2(s[2 * i + 2], s[2 * i + 3]), mul2, negm2);
+        const float p0 = ex2(f2_lo(a01)), p1 = ex2(f2_hi(a01));
+        const float p2 = ex2(f2_lo(a23)), p3 = ex2(f2_hi(a23));
+        sum01 = fadd2(sum01, f2(p0, p1));
+        sum23 = fadd2(sum23, f2(p2, p3));
         pk[i] = P2::pack(p0, p1);
         pk[i + 1] = P2::pack(p2, p3);
       }
-      l += (sum0 + sum1) + (sum2 + sum3);
+      l += (f2_lo(sum01) + f2_hi(sum01)) + (f2_lo(sum23) + f2_hi(sum23));
       if (tid == 0) TR(0, g, 8);
       // P (16 bit) over the S columns: this quarter's 32 keys -> 16 packed columns
       tmem_st16(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 16), pk);
