@@ -388,36 +388,72 @@ def main():
     if not args.no_e2e:
         hq, hk, hv, hdo = (t.detach().to("cpu").pin_memory() for t in (q, k, v, do))
         hb = bias.detach().to("cpu").pin_memory() if bias is not None else None
-        ho = torch.empty_like(hq)
-        hdq, hdk, hdv = torch.empty_like(hq), torch.empty_like(hk), torch.empty_like(hv)
-        hdb = torch.empty_like(hb) if trainable else None
+        pinned_like = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        ho = pinned_like(hq)
+        hdq, hdk, hdv = pinned_like(hq), pinned_like(hk), pinned_like(hv)
+        hdb = pinned_like(hb) if trainable else None
         h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo)) + (hb.numel() * hb.element_size() if hb is not None else 0)
         d2h = sum(t.numel() * t.element_size() for t in (ho, hdq, hdk, hdv)) + (hdb.numel() * hdb.element_size() if hdb is not None else 0)
 
-        def e2e_step():
-            dq_ = hq.to(device, non_blocking=True).requires_grad_()
-            dk_ = hk.to(device, non_blocking=True).requires_grad_()
-            dv_ = hv.to(device, non_blocking=True).requires_grad_()
-            ddo = hdo.to(device, non_blocking=True)
-            db = hb.to(device, non_blocking=True) if hb is not None else None
-            if trainable:
-                db.requires_grad_()
-            out = flash_attention_fn(dq_, dk_, dv_, db, w["causal"], None)
-            out.backward(ddo)
-            ho.copy_(out.detach(), non_blocking=True)
-            hdq.copy_(dq_.grad, non_blocking=True)
-            hdk.copy_(dk_.grad, non_blocking=True)
-            hdv.copy_(dv_.grad, non_blocking=True)
-            if trainable:
-                hdb.copy_(db.grad, non_blocking=True)
+        # Three streams: copies in, compute (the public API call), copies out.  Device inputs are
+        # double-buffered, so the H2D copy of step i+1 and the D2H copy of step i run while step
+        # i / i+1 computes; every step still copies all of its inputs in and all of its results out.
+        main = torch.cuda.current_stream(device)
+        s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        slots = []
+        for _ in range(2):
+            d = {"q": torch.empty_like(q).requires_grad_(), "k": torch.empty_like(k).requires_grad_(),
+                 "v": torch.empty_like(v).requires_grad_(), "do": torch.empty_like(do),
+                 "b": None, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "keep": None}
+            if hb is not None:
+                d["b"] = torch.empty_like(bias.detach())
+                if trainable:
+                    d["b"].requires_grad_()
+            d["done"].record(main)
+            slots.append(d)
 
-        e2e_steps = max(2, min(args.steps, 5))
-        e2e_step()
+        def e2e_step(i):
+            d = slots[i & 1]
+            with torch.cuda.stream(s_in), torch.no_grad():
+                s_in.wait_event(d["done"])  # the step that last used this slot has finished
+                d["q"].copy_(hq, non_blocking=True)
+                d["k"].copy_(hk, non_blocking=True)
+                d["v"].copy_(hv, non_blocking=True)
+                d["do"].copy_(hdo, non_blocking=True)
+                if hb is not None:
+                    d["b"].copy_(hb, non_blocking=True)
+                d["in"].record(s_in)
+            main.wait_event(d["in"])
+            out = flash_attention_fn(d["q"], d["k"], d["v"], d["b"], w["causal"], None)
+            out.backward(d["do"])
+            d["done"].record(main)
+            res = [out.detach(), d["q"].grad, d["k"].grad, d["v"].grad]
+            dst = [ho, hdq, hdk, hdv]
+            if trainable:
+                res.append(d["b"].grad)
+                dst.append(hdb)
+                d["b"].grad = None
+            d["q"].grad = d["k"].grad = d["v"].grad = None
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(d["done"])
+                for src, h in zip(res, dst):
+                    src.record_stream(s_out)
+                    h.copy_(src, non_blocking=True)
+
+        def e2e_drain():
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        e2e_steps = max(2, min(args.steps, 8))
+        e2e_step(0)
+        e2e_step(1)
+        e2e_drain()
         barrier()
         s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s2.record()
-        for _ in range(e2e_steps):
-            e2e_step()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_drain()
         e2.record()
         barrier()
         ms2 = s2.elapsed_time(e2) / e2e_steps
@@ -426,7 +462,10 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms2 = t.item()
         e2e = {"value": total_flops / (ms2 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms2,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "pipeline": "3 streams, double-buffered device inputs: H2D of step i+1 and D2H of step i "
+                           "overlap compute; the drain of the last copies is inside the timed region"}
+        del slots
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

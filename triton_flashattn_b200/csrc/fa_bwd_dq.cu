@@ -257,15 +257,22 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       if (lane == 0) mbar_arrive(&s_free);
 
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 32; i += 2) {
+        f32x2 a;
         if (BIAS == 1) {
           const float2 f = P2::unpack(bcur.w[i >> 1]);
-          pr[i] = ex2(fmaf(pr[i], p.scale_log2, fmaf((i & 1) ? f.y : f.x, kLog2e, neg_lse)));
-        } else if (BIAS == 2) {
-          const bool keep = ((bcur.w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0;
-          pr[i] = keep ? ex2(fmaf(pr[i], p.scale_log2, neg_lse)) : 0.f;
+          a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
+                    ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
         } else {
-          pr[i] = ex2(fmaf(pr[i], p.scale_log2, neg_lse));
+          a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+        }
+        if (BIAS == 2) {
+          const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
+          pr[i] = (m2 & 0xFFu) != 0 ? ex2(f2_lo(a)) : 0.f;
+          pr[i + 1] = (m2 & 0xFF00u) != 0 ? ex2(f2_hi(a)) : 0.f;
+        } else {
+          pr[i] = ex2(f2_lo(a));
+          pr[i + 1] = ex2(f2_hi(a));
         }
       }
       if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
@@ -294,9 +301,10 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
         if (lane == 0) mbar_arrive(&dp_free);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float d0 = pr[2 * i] * (__uint_as_float(dp[2 * i]) - delta_r);
-          const float d1 = pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - delta_r);
-          dsu[i] = P2::pack(d0, d1);
+          const f32x2 d = fmul2(f2(pr[2 * i], pr[2 * i + 1]),
+                                fadd2(f2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1])),
+                                      f2(-delta_r, -delta_r)));
+          dsu[i] = P2::pack(f2_lo(d), f2_hi(d));
         }
       }
       if (j >= 1) {
