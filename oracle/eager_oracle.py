@@ -112,8 +112,8 @@ def attention_backward(q, k, v, bias, causal, sm_scale, do, o_saved=None):
 
 def attention_autograd(q, k, v, bias, causal, sm_scale, do):
     """Same quantities through torch.autograd on the plain eager expression
-    softmax(q k^T * scale + bias) v -- the form BASELINE names as the fallback
-    reference.  Used to cross-check attention_backward."""
+    softmax(q k^T * scale + bias) v in fp32 (the textbook reference for this
+    operator).  Used to cross-check attention_backward."""
     D = q.shape[-1]
     sm_scale = D ** -0.5 if sm_scale is None else sm_scale
     qf = q.detach().float().requires_grad_()

@@ -21,7 +21,7 @@ os.environ["TRITON_INTERPRET"] = "1"
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_DIR", "/root/reference")
+REF = os.environ["REFERENCE_DIR"]  # checkout of sukjunhwang/triton_flashattn
 sys.path.insert(0, REF)
 import flash_attention as ref  # noqa: E402
 
