@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           const uint32_t q_par = (gs >> 1) & 1, do_par = (gs / kDoStages) & 1;
           // S_gs: its columns are free once the row threads hold S_{gs-1} in registers
           const uint32_t pq = mbar_poll(&q_full[qs], q_par);
-          if (gs >= 1) ok = mbar_wait(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
+          if (gs >= 1) ok = mbar_wait_hot(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
           if (ok) ok = wait_polled(pq, &q_full[qs], q_par, ctx, kSiteQFull, t);
           if (!ok) break;
           TR(1, gs, 1);
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           TR(1, gs, 2);
           // dP_gs: same for the dP columns; dO_gs replaces dO_{gs-1} after dV_{gs-1} when
           // single-staged
-          if (gs >= 1) ok = mbar_wait(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
+          if (gs >= 1) ok = mbar_wait_hot(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
           if (ok) ok = wait_polled(pdo, &do_full[ds], do_par, ctx, kSiteDoFull, t);
           if (!ok) break;
           TR(1, gs, 3);
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           // row warps after they have read the previous tile's accumulators.
           const uint32_t pdo = mbar_poll(&do_full[ds], (gs / kDoStages) & 1);
           const uint32_t pq = mbar_poll(&q_full[qs], (gs >> 1) & 1);
-          ok = mbar_wait(&p_ready, gs & 1, ctx, kSitePReady, t);
+          ok = mbar_wait_hot(&p_ready, gs & 1, ctx, kSitePReady, t);
           if (ok) ok = wait_polled(pdo, &do_full[ds], (gs / kDoStages) & 1, ctx, kSiteDoFull, t);
           if (!ok) break;
           TR(2, gs, 1);
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           mma_commit(&dv_done);
           TR(2, gs, 2);
           // dK += dS^T Q
-          ok = mbar_wait(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
+          ok = mbar_wait_hot(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
           if (ok) ok = wait_polled(pq, &q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
           if (!ok) break;
           TR(2, gs, 3);
@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         const bool two = n0 + 64 < p.N;
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
-          if (gs >= 1) ok = mbar_wait(&dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
+          if (gs >= 1) ok = mbar_wait_hot(&dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
           if (!ok) break;
           const int m0 = (i_start + t) * 128;
           mbar_expect_tx(&bias_full, two ? 2 * kBlk : kBlk);

@@ -199,6 +199,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return mbar_wait_slow(bar, parity, ctx, site, iter);
 }
 
+// Wait of a single-lane control role that sits on the critical path: polls the phase
+// without suspending (a suspended try_wait wakes up a few hundred cycles after the phase
+// completes), then falls back to the bounded wait.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+                                              int site, int iter = 0) {
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_poll(bar, parity)) return true;
+  return mbar_wait(bar, parity, ctx, site, iter);
+}
+
 // ----------------------------------------------------------------------------
 // proxies and fences
 // ----------------------------------------------------------------------------

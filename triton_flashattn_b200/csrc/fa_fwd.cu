@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           // the barrier can never run two phases ahead of this wait, however long the issuer
           // sat in another wait (a new tile's Q) in between.
           if (g >= 2)
-            ok = mbar_wait(&pv_done[st], ((g >> 1) - 1) & 1, ctx, kSitePvDoneQK, j);
+            ok = mbar_wait_hot(&pv_done[st], ((g >> 1) - 1) & 1, ctx, kSitePvDoneQK, j);
           if (ok && j == 0) ok = mbar_wait(&q_full, it & 1, ctx, kSiteQ, it);
           if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
           if (!ok) break;
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           const uint32_t pv = mbar_poll(&v_full[st], (g >> 1) & 1);
           // P_g of a new tile is only announced after all sixteen softmax warps have read
           // the previous tile's O, so the first product of a tile may overwrite it
-          ok = mbar_wait(&p_full, g & 1, ctx, kSitePFull, j);
+          ok = mbar_wait_hot(&p_full, g & 1, ctx, kSitePFull, j);
           if (ok) ok = wait_polled(pv, &v_full[st], (g >> 1) & 1, ctx, kSiteVFull, j);
           if (!ok) break;
           TR(1, g, 4);
