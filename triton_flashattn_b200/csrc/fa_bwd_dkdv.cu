@@ -503,21 +503,25 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
               const int i = c * 8 + e * 2;
               const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
                                     ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
-              pr[i] = ex2(f2_lo(a));
-              pr[i + 1] = ex2(f2_hi(a));
+              // every fourth pair on the FMA pipe, the rest on the special-function unit
+              const f32x2 pe = (e == 1) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
+              pr[i] = f2_lo(pe);
+              pr[i + 1] = f2_hi(pe);
             }
           }
         } else {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+          // every fourth pair on the FMA pipe, the rest on the special-function unit
+          const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
           if (BK == 2) {
             const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
-            pr[i] = (m2 & 0xFFu) != 0 ? ex2(f2_lo(a)) : 0.f;
-            pr[i + 1] = (m2 & 0xFF00u) != 0 ? ex2(f2_hi(a)) : 0.f;
+            pr[i] = (m2 & 0xFFu) != 0 ? f2_lo(pe) : 0.f;
+            pr[i + 1] = (m2 & 0xFF00u) != 0 ? f2_hi(pe) : 0.f;
           } else {
-            pr[i] = ex2(f2_lo(a));
-            pr[i + 1] = ex2(f2_hi(a));
+            pr[i] = f2_lo(pe);
+            pr[i + 1] = f2_hi(pe);
           }
         }
         }
