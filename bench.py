@@ -63,7 +63,7 @@ def load_peaks():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one dkdv_kernel launch of config 3 at B=2,
 # divided by 2 (ncu capture summarised in profiles/dkdv_kernel_config3_b2_ncu_full.md)
-DKDV_DRAM_BYTES_PER_BATCH_CONFIG3 = (341.48e6 + 260.54e6) / 2
+DKDV_DRAM_BYTES_PER_BATCH_CONFIG3 = (340.52e6 + 260.69e6) / 2
 
 
 def flops(w, which):
@@ -375,7 +375,7 @@ def main():
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kd["gbs"] / peaks["hbm_gbs"], 3),
                             "traffic": None, "peak_source": peaks["source"]}
             # DRAM traffic of one dK/dV launch: from the ncu capture of this workload at B=2
-            # (profiles/dkdv_kernel_config3_b2_ncu_full.md: 341.5 MB read + 260.5 MB written);
+            # (profiles/dkdv_kernel_config3_b2_ncu_full.md: 340.5 MB read + 260.7 MB written);
             # the kernel's traffic is proportional to B
             if args.workload == "3" and not args.bias:
                 roofline["traffic"] = int(DKDV_DRAM_BYTES_PER_BATCH_CONFIG3 * w["B"])
