@@ -312,6 +312,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       // wait fall two phases behind.)  The wait for the store's read sits right after the
       // store: the next thing this thread needs, P of the next step, is further away.
       const bool stores_here = BIAS == 1 && p.write_dbias;
+      bool zeros_in_flight = false;
       bool ok = true;
       uint32_t g = 0;
       int bh, nb, i_start, T_steps;
@@ -326,8 +327,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
               tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
           }
           tma_store_commit();
-          tma_store_wait_read<0>();
-          mbar_arrive(&st_done);
+          // the zero tiles are read out of sDS while P of the first step is formed and dV is
+          // issued; their completion is announced just before this thread needs dS
+          zeros_in_flight = true;
+          if (T_steps <= 0) {
+            tma_store_wait_read<0>();
+            mbar_arrive(&st_done);
+            zeros_in_flight = false;
+          }
         }
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
@@ -348,6 +355,11 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           mma_commit(&do_empty[ds]);
           mma_commit(&dv_done);
           TR(2, gs, 2);
+          if (zeros_in_flight) {
+            tma_store_wait_read<0>();
+            mbar_arrive(&st_done);
+            zeros_in_flight = false;
+          }
           // dK += dS^T Q
           ok = mbar_wait_hot(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
           if (ok) ok = wait_polled(pq, &q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
