@@ -502,7 +502,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         if (lane == 0) mbar_arrive(&s_free);
         // P = exp2(S * scale * log2e + bias * log2e - LSE2); rows beyond M have LSE2 = +inf
         if constexpr (BIAS == 1) {
-          // the bias tile sits where this thread's P chunks go
+          // the bias tile sits where this thread's P chunks go; what does not need it is
+          // computed while it travels: x = S * scale * log2e - LSE2
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const f32x2 x = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+            pr[i] = f2_lo(x);
+            pr[i + 1] = f2_hi(x);
+          }
           ok = wait_warp_polled(pb, &bias_full, gs & 1, ctx, kSiteBiasFull, t);
           if (!ok) break;
 #pragma unroll
@@ -513,8 +520,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
             for (int e = 0; e < 4; ++e) {
               const float2 f = P2::unpack(w[e]);
               const int i = c * 8 + e * 2;
-              const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
-                                    ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
+              const f32x2 a = ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(pr[i], pr[i + 1]));
               // every fourth pair on the FMA pipe, the rest on the special-function unit
               const f32x2 pe = (e == 1) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
               pr[i] = f2_lo(pe);
