@@ -1,7 +1,9 @@
 // dQ kernels for sm_100a.
 //
 // (1) dq_recompute_kernel -- general path (no bias, bool mask, float bias).
-// One CTA owns 128 query rows of one (batch, head) and walks the key blocks.
+// Persistent, one CTA per SM, scheduled like the forward kernel: a tile is 128 query
+// rows of one (batch, head); a CTA walks its tiles and, inside a tile, the key blocks;
+// rings, tensor-memory buffers and barrier phases carry on from tile to tile.
 // Roles (608 threads): warps 0-15 row threads (lanes 32*(w&3).., key quarter w>>2),
 // warp 16 TMA producer, warp 17 MMA issuer for S and dP (tensor-memory owner),
 // warp 18 MMA issuer for dQ.  Per key block:
@@ -40,6 +42,7 @@ struct DqParams {
   int64_t bias_sB, bias_sH, bias_sM;
   int64_t dq_sB, dq_sM, dq_sH;
   int H, M, N, D;
+  int n_mblk, n_tiles;  // query blocks per (batch, head); tiles = n_mblk * B * H
   int causal, bias_vec32;
   float scale_log2;
   float sm_scale;
@@ -47,7 +50,7 @@ struct DqParams {
 
 enum DqSite { kSiteQdo = 1, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty, kSiteSFull,
               kSiteDpFull, kSiteSFree, kSiteDpFree, kSiteDsReady, kSiteDqDone, kSiteEpilogue,
-              kSiteStageFull, kSiteStageEmpty };
+              kSiteStageFull, kSiteStageEmpty, kSiteQdoEmpty };
 
 template <int DP>
 struct DqSmem {
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t qdo_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ uint64_t qdo_full, qdo_empty, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ uint64_t s_full, dp_full, s_free, dp_free, ds_ready, dq_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -81,19 +84,31 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int m_block = gridDim.x - 1 - blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / p.H;
-  const int h = bh - b * p.H;
-  const int m0 = m_block * 128;
-  int nblk = (p.N + 127) >> 7;
-  if (p.causal) nblk = min(nblk, m_block + 1);
+
+  // Persistent CTA with the schedule of the forward kernel: tiles (128 query rows of one
+  // (batch, head)) are numbered (batch*head)-major, CTA c takes units c, c+G, ...; a unit is
+  // one tile or - causal - a heavy and a light tile of the same (batch, head).  All roles keep
+  // running counters, so rings, tensor-memory buffers and barrier phases carry on from tile to
+  // tile and the next tile's loads and first products overlap the current tile's epilogue.
+  const int nblk_all = (p.N + 127) >> 7;
+  const int sched_sh = p.causal ? 1 : 0;
+  auto tile_at = [&](int it, int& bh, int& m_block, int& nblk) -> bool {
+    const int u = static_cast<int>(blockIdx.x) + (it >> sched_sh) * static_cast<int>(gridDim.x);
+    const int k = (u << sched_sh) + (it & sched_sh);
+    if (k >= p.n_tiles) return false;
+    bh = k / p.n_mblk;
+    const int pos = k - bh * p.n_mblk;
+    m_block = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_mblk - 1 - (pos >> 1)) : pos;
+    nblk = p.causal ? min(nblk_all, m_block + 1) : nblk_all;
+    return true;
+  };
 
   WaitCtx ctx{&abort_flag, p.status, 3};
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&qdo_full, 1);
+    mbar_init(&qdo_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 2);  // S_j and dQ_j both read K_j
@@ -127,27 +142,37 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
       tma_prefetch_desc(&p.map_do);
-      mbar_expect_tx(&qdo_full, 2 * L::kTile);
-      for (int kb = 0; kb < KB; ++kb) {
-        tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
-        tma_load_4d(smem + L::kDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
-      }
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        const int n0 = j * 128;
-        if (j >= 2) ok = mbar_wait(&k_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+      uint32_t gj = 0;  // key blocks issued so far, over all tiles
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
+        // Q and dO are single tiles: free once the previous tile's last S and dP are through
+        if (it >= 1) ok = mbar_wait(&qdo_empty, (it - 1) & 1, ctx, kSiteQdoEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&k_full[st], L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
-                      n0, b);
-        if (j >= 2) ok = mbar_wait(&v_empty[st], ((j >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
-        if (!ok) break;
-        mbar_expect_tx(&v_full[st], L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
-                      n0, b);
+        mbar_expect_tx(&qdo_full, 2 * L::kTile);
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
+          tma_load_4d(smem + L::kDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
+        }
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const int n0 = j * 128;
+          if (g >= 2) ok = mbar_wait(&k_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+          if (!ok) break;
+          mbar_expect_tx(&k_full[st], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
+                        n0, b);
+          if (g >= 2) ok = mbar_wait(&v_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
+          if (!ok) break;
+          mbar_expect_tx(&v_full[st], L::kTile);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
+                        n0, b);
+        }
+        gj += nblk;
       }
     }
   } else if (warp == 17) {
@@ -160,44 +185,37 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       const uint64_t q_km = make_sdesc(q_addr, 0, 1024), do_km = make_sdesc(do_addr, 0, 1024);
       const uint64_t k_km_0 = make_sdesc(k_addr, 0, 1024), k_km_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
       const uint64_t v_km_0 = make_sdesc(v_addr, 0, 1024), v_km_1 = make_sdesc(v_addr + L::kTile, 0, 1024);
-      auto issue_s = [&](int j) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, (j & 1) ? k_km_1 : k_km_0, kBlk, kBlk,
-                                          idesc_s, false);
-        mma_commit(&s_full);
-        mma_commit(&k_empty[j & 1]);
-      };
-      auto issue_dp = [&](int j) {
-        issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, (j & 1) ? v_km_1 : v_km_0, kBlk, kBlk,
-                                          idesc_s, false);
-        mma_commit(&dp_full);
-        mma_commit(&v_empty[j & 1]);
-      };
-      bool ok = mbar_wait(&qdo_full, 0, ctx, kSiteQdo, 0);
-      if (ok) ok = mbar_wait(&k_full[0], 0, ctx, kSiteKFull, 0);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        ok = mbar_wait(&v_full[0], 0, ctx, kSiteVFull, 0);
-      }
-      if (ok) {
-        tc_fence_after();
-        issue_dp(0);
-      }
-      for (int j = 0; j + 1 < nblk && ok; ++j) {
-        const int st1 = (j + 1) & 1;
-        const uint32_t ph1 = ((j + 1) >> 1) & 1;
-        const uint32_t pk = mbar_poll(&k_full[st1], ph1);
-        const uint32_t pv = mbar_poll(&v_full[st1], ph1);
-        ok = mbar_wait(&s_free, j & 1, ctx, kSiteSFree, j);
-        if (ok) ok = wait_polled(pk, &k_full[st1], ph1, ctx, kSiteKFull, j + 1);
-        if (!ok) break;
-        tc_fence_after();
-        issue_s(j + 1);
-        ok = mbar_wait(&dp_free, j & 1, ctx, kSiteDpFree, j);
-        if (ok) ok = wait_polled(pv, &v_full[st1], ph1, ctx, kSiteVFull, j + 1);
-        if (!ok) break;
-        tc_fence_after();
-        issue_dp(j + 1);
+      bool ok = true;
+      uint32_t gj = 0;
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          const uint32_t pk = mbar_poll(&k_full[st], ph);
+          const uint32_t pv = mbar_poll(&v_full[st], ph);
+          // S_g: its columns are free once the row threads hold S_{g-1} in registers
+          if (g >= 1) ok = mbar_wait_hot(&s_free, (g - 1) & 1, ctx, kSiteSFree, j);
+          if (ok && j == 0) ok = mbar_wait(&qdo_full, it & 1, ctx, kSiteQdo, it);
+          if (ok) ok = wait_polled(pk, &k_full[st], ph, ctx, kSiteKFull, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, st ? k_km_1 : k_km_0, kBlk, kBlk,
+                                            idesc_s, false);
+          mma_commit(&s_full);
+          mma_commit(&k_empty[st]);
+          if (g >= 1) ok = mbar_wait_hot(&dp_free, (g - 1) & 1, ctx, kSiteDpFree, j);
+          if (ok) ok = wait_polled(pv, &v_full[st], ph, ctx, kSiteVFull, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, st ? v_km_1 : v_km_0, kBlk, kBlk,
+                                            idesc_s, false);
+          mma_commit(&dp_full);
+          mma_commit(&v_empty[st]);
+          if (j == nblk - 1) mma_commit(&qdo_empty);  // Q and dO may be replaced
+        }
+        gj += nblk;
       }
     }
     __syncwarp();
@@ -209,17 +227,25 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       const uint64_t k_mn_0 = make_sdesc(k_addr, kBlk, 1024), k_mn_1 = make_sdesc(k_addr + L::kTile, kBlk, 1024);
       const uint64_t ds_km = make_sdesc(smem_u32(smem + L::kDs), 0, 1024);
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t pk = mbar_poll(&k_full[st], (j >> 1) & 1);
-        ok = mbar_wait(&ds_ready, j & 1, ctx, kSiteDsReady, j);
-        if (ok) ok = wait_polled(pk, &k_full[st], (j >> 1) & 1, ctx, kSiteKFull, j);
-        if (!ok) break;
-        tc_fence_after();
-        issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, st ? k_mn_1 : k_mn_0, kBlk, kBlk, idesc_dq,
-                                      j > 0);
-        mma_commit(&k_empty[st]);
-        mma_commit(&dq_done);
+      uint32_t gj = 0;
+      int bh, m_block, nblk;
+      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+        for (int j = 0; j < nblk && ok; ++j) {
+          const uint32_t g = gj + j;
+          const int st = g & 1;
+          const uint32_t pk = mbar_poll(&k_full[st], (g >> 1) & 1);
+          // dS of a new tile is only announced by all sixteen row warps after they have read
+          // the previous tile's dQ, so the first product of a tile may overwrite it
+          ok = mbar_wait_hot(&ds_ready, g & 1, ctx, kSiteDsReady, j);
+          if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
+          if (!ok) break;
+          tc_fence_after();
+          issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, st ? k_mn_1 : k_mn_0, kBlk, kBlk, idesc_dq,
+                                        j > 0);
+          mma_commit(&k_empty[st]);
+          mma_commit(&dq_done);
+        }
+        gj += nblk;
       }
     }
     __syncwarp();
@@ -228,103 +254,113 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
     const int r = (warp & 3) * 32 + lane;
     const int qt = warp >> 2;  // key quarter of every block
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
-    const int m = m0 + r;
-    const bool row_ok = m < p.M;
     bool ok = live;
     uint8_t* sDS = smem + L::kDs + (qt >> 1) * kBlk;
     const int chunk0 = (qt & 1) * 4;
-    const int64_t bias_row = b * p.bias_sB + h * p.bias_sH + (int64_t)m * p.bias_sM;
-    const float neg_lse = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
-    const float delta_r = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
-    BiasRegs<BIAS> bnext;
-    if (ok && BIAS != 0)
-      load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, qt * 32, p.N, p.bias_vec32 != 0);
+    uint32_t gj = 0;
+    int bh, m_block, nblk;
+    for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
+      const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
+      const int m = m0 + r;
+      const bool row_ok = m < p.M;
+      const int64_t bias_row = b * p.bias_sB + h * p.bias_sH + (int64_t)m * p.bias_sM;
+      const float neg_lse = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
+      const float delta_r = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
+      BiasRegs<BIAS> bnext;
+      if (BIAS != 0)
+        load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, qt * 32, p.N, p.bias_vec32 != 0);
 
-    for (int j = 0; j < nblk && ok; ++j) {
-      const int col0 = j * 128 + qt * 32;
-      BiasRegs<BIAS> bcur = bnext;
-      if (BIAS != 0 && j + 1 < nblk)
-        load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, col0 + 128, p.N, p.bias_vec32 != 0);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const uint32_t g = gj + j;
+        const int col0 = j * 128 + qt * 32;
+        BiasRegs<BIAS> bcur = bnext;
+        if (BIAS != 0 && j + 1 < nblk)
+          load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, col0 + 128, p.N, p.bias_vec32 != 0);
 
-      ok = wait_warp(&s_full, j & 1, ctx, kSiteSFull, j);
-      if (!ok) break;
-      tc_fence_after();
-      float pr[32];
-      tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free);
-
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        f32x2 a;
-        if (BIAS == 1) {
-          const float2 f = P2::unpack(bcur.w[i >> 1]);
-          a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
-                    ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
-        } else {
-          a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
-        }
-        // every fourth pair on the FMA pipe, the rest on the special-function unit
-        const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
-        if (BIAS == 2) {
-          const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
-          pr[i] = (m2 & 0xFFu) != 0 ? f2_lo(pe) : 0.f;
-          pr[i + 1] = (m2 & 0xFF00u) != 0 ? f2_hi(pe) : 0.f;
-        } else {
-          pr[i] = f2_lo(pe);
-          pr[i + 1] = f2_hi(pe);
-        }
-      }
-      if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
-        int limit = p.N - col0;
-        if (p.causal) limit = min(limit, m - col0 + 1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= limit) pr[i] = 0.f;
-      }
-
-      uint32_t pdp = 0, pdq = 1;
-      if (j >= 1)
-        mbar_poll2(&dp_full, j & 1, &dq_done, (j - 1) & 1, pdp, pdq);
-      else
-        pdp = mbar_poll(&dp_full, j & 1);
-      ok = wait_warp_polled(pdp, &dp_full, j & 1, ctx, kSiteDpFull, j);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t dsu[16];
-      {
-        uint32_t dp[32];
-        tmem_ld32(tmem_addr(tmem, lane_base, kColDp + qt * 32), dp);
+        ok = wait_warp(&s_full, g & 1, ctx, kSiteSFull, j);
+        if (!ok) break;
+        tc_fence_after();
+        float pr[32];
+        tmem_ld32(tmem_addr(tmem, lane_base, kColS + qt * 32), reinterpret_cast<uint32_t*>(pr));
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&dp_free);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const f32x2 d = fmul2(f2(pr[2 * i], pr[2 * i + 1]),
-                                fadd2(f2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1])),
-                                      f2(-delta_r, -delta_r)));
-          dsu[i] = P2::pack(f2_lo(d), f2_hi(d));
-        }
-      }
-      if (j >= 1) {
-        ok = wait_warp_polled(pdq, &dq_done, (j - 1) & 1, ctx, kSiteDqDone, j);
-        if (!ok) break;
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + swz_off(r, chunk0 + c)) = v;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_ready);
-    }
+        if (lane == 0) mbar_arrive(&s_free);
 
-    if (ok) ok = wait_warp(&dq_done, (nblk - 1) & 1, ctx, kSiteEpilogue, nblk);
-    if (ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          f32x2 a;
+          if (BIAS == 1) {
+            const float2 f = P2::unpack(bcur.w[i >> 1]);
+            a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2),
+                      ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(neg_lse, neg_lse)));
+          } else {
+            a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+          }
+          // every fourth pair on the FMA pipe, the rest on the special-function unit
+          const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
+          if (BIAS == 2) {
+            const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
+            pr[i] = (m2 & 0xFFu) != 0 ? f2_lo(pe) : 0.f;
+            pr[i + 1] = (m2 & 0xFF00u) != 0 ? f2_hi(pe) : 0.f;
+          } else {
+            pr[i] = f2_lo(pe);
+            pr[i + 1] = f2_hi(pe);
+          }
+        }
+        if ((col0 + 32 > p.N) || (p.causal && col0 + 31 > m0)) {
+          int limit = p.N - col0;
+          if (p.causal) limit = min(limit, m - col0 + 1);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i >= limit) pr[i] = 0.f;
+        }
+
+        uint32_t pdp = 0, pdq = 1;
+        if (j >= 1)
+          mbar_poll2(&dp_full, g & 1, &dq_done, (g - 1) & 1, pdp, pdq);
+        else
+          pdp = mbar_poll(&dp_full, g & 1);
+        ok = wait_warp_polled(pdp, &dp_full, g & 1, ctx, kSiteDpFull, j);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t dsu[16];
+        {
+          uint32_t dp[32];
+          tmem_ld32(tmem_addr(tmem, lane_base, kColDp + qt * 32), dp);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&dp_free);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const f32x2 d = fmul2(f2(pr[2 * i], pr[2 * i + 1]),
+                                  fadd2(f2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1])),
+                                        f2(-delta_r, -delta_r)));
+            dsu[i] = P2::pack(f2_lo(d), f2_hi(d));
+          }
+        }
+        // the previous dQ product has read sDS (for the first block of a tile its barrier was
+        // seen in the previous tile's epilogue)
+        if (j >= 1) {
+          ok = wait_warp_polled(pdq, &dq_done, (g - 1) & 1, ctx, kSiteDqDone, j);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 v = make_uint4(dsu[c * 4 + 0], dsu[c * 4 + 1], dsu[c * 4 + 2], dsu[c * 4 + 3]);
+          *reinterpret_cast<uint4*>(sDS + swz_off(r, chunk0 + c)) = v;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_ready);
+      }
+      if (!ok) break;
+      gj += nblk;
+
+      // ---- epilogue: dQ * sm_scale -> global
+      ok = wait_warp(&dq_done, (gj - 1) & 1, ctx, kSiteEpilogue, nblk);
+      if (!ok) break;
       tc_fence_after();
       constexpr int kQD = DP / 4;
       const int d0 = qt * kQD;
@@ -332,6 +368,8 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       uint32_t a[kQD];
       tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColDq + d0), a);
       tmem_ld_wait();
+      // dQ is in registers: the next tile's first product may overwrite it
+      tc_fence_before();
       if (row_ok) {
 #pragma unroll
         for (int c = 0; c < kQD / 8; ++c) {
@@ -489,7 +527,8 @@ int configure(K kern, int smem_bytes, bool* configured) {
 }
 
 template <int DP, typename T, int BIAS>
-int launch_recompute(const DqParams& kp, dim3 grid, cudaStream_t stream) {
+int launch_recompute(const DqParams& kp, dim3 /*tile_grid*/, cudaStream_t stream) {
+  const dim3 grid(persistent_grid(kp.causal ? (kp.n_tiles + 1) / 2 : kp.n_tiles));
   using L = DqSmem<DP>;
   static bool configured[64] = {};
   auto kern = dq_recompute_kernel<DP, T, BIAS>;
@@ -579,7 +618,9 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   }
   kp.scale_log2 = p.sm_scale * kLog2e;
   kp.sm_scale = p.sm_scale;
-  const dim3 grid((p.M + 127) / 128, p.B * p.H);
+  kp.n_mblk = (p.M + 127) / 128;
+  kp.n_tiles = kp.n_mblk * p.B * p.H;
+  const dim3 grid((p.M + 127) / 128, p.B * p.H);  // streamed-dS variant: one CTA per tile
   const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {
     return dp == 64 ? launch_bias<64, __nv_bfloat16>(kp, p.bias_kind, from_ds, grid, stream)
