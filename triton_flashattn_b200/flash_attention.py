@@ -30,17 +30,16 @@ _HEAD_DIMS = {16, 32, 64, 128, 256}
 
 
 def _stride3(t: torch.Tensor):
-    return _cabi._I64x3(t.stride(0), t.stride(1), t.stride(2))
+    st = t.stride()
+    return _cabi._I64x3(st[0], st[1], st[2])
 
 
 def _tile_ready(t: torch.Tensor) -> torch.Tensor:
     """(B, S, H, D) operand as the kernels need it: unit inner stride, every other
     stride and the base address a multiple of 16 bytes.  Copies only when needed."""
-    ok = (
-        t.stride(3) == 1
-        and all(s % 8 == 0 and s > 0 for s in t.stride()[:3])
-        and t.data_ptr() % 16 == 0
-    )
+    s0, s1, s2, s3 = t.stride()
+    ok = (s3 == 1 and s0 > 0 and s1 > 0 and s2 > 0 and (s0 | s1 | s2) % 8 == 0
+          and t.data_ptr() % 16 == 0)
     return t if ok else t.contiguous()
 
 
@@ -127,7 +126,15 @@ def _params(q, k, v, o, lse, bias_t, bias_kind, causal, sm_scale):
     return p
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: torch.Tensor):
+    """Handle of the current CUDA stream of t's device (the raw getter is ~10x cheaper than
+    building a torch.cuda.Stream object on every call)."""
+    if _raw_stream is not None:
+        idx = t.device.index
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device() if idx is None else idx))
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
