@@ -119,51 +119,82 @@ def make_inputs(w, device, seed, pin=False):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while a region runs."""
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 20 ms.  Only samples whose
+    time stamp falls inside the marked region (the timed steps) are used; if the region was too
+    short to catch one, the nearest samples are used instead and `in_region` says 0."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
+        self.first = ""
+        self.t0 = self.t1 = None
 
     def start(self):
+        """Starts the sampler and waits (at most 10 s) for its first line, so that the start-up
+        of nvidia-smi (driver initialisation on every GPU of the machine) is over before the
+        timed region begins and only the cheap periodic queries fall into it."""
+        import select
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            if select.select([self.proc.stdout], [], [], 10.0)[0]:
+                self.first = self.proc.stdout.readline()
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        import datetime
+        self.t0 = datetime.datetime.now()
+
+    def mark_end(self):
+        import datetime
+        self.t1 = datetime.datetime.now()
+
     def stop(self):
+        import datetime
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
-        for line in out.strip().splitlines():
+        rows = []
+        for line in (self.first + out).strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((ts, float(f[1]), float(f[2]), f[5:9]))
             except ValueError:
                 continue
+        inside = rows
+        if self.t0 is not None and self.t1 is not None:
+            pad = datetime.timedelta(milliseconds=10)
+            inside = [r for r in rows if self.t0 - pad <= r[0] <= self.t1 + pad]
+        in_region = len(inside)
+        if not inside and rows and self.t0 is not None:
+            mid = self.t0 + (self.t1 - self.t0) / 2
+            inside = sorted(rows, key=lambda r: abs((r[0] - mid).total_seconds()))[:2]
+        sm = [r[1] for r in inside]
+        smax = [r[2] for r in inside]
+        reasons = set()
+        for r in inside:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                 f[5:9]):
+                                 r[3]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "in_region": in_region, "reasons": sorted(reasons)}
 
 
 def cuda_time_ms(fn, iters, stream_sync=True):
@@ -305,11 +336,13 @@ def main():
     sampler.start()  # every rank watches its own GPU
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     start.record()
     for _ in range(args.steps):
         step()
     end.record()
     barrier()
+    sampler.mark_end()
     ms = start.elapsed_time(end) / args.steps
     clocks = sampler.stop()
     ranks = None
