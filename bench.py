@@ -13,8 +13,8 @@ Rank 0 prints one JSON line:
   value        fwd+bwd TFLOP/s, inputs resident in HBM, through the public Python API
   e2e          same metric with HOST (pinned) inputs and outputs: H2D of q,k,v,bias,do
                and D2H of out,dq,dk,dv,dbias inside the timed region
-  roofline     dominant kernel (dK/dV) against the measured tensor peak, timed alone
-               with CUDA events through the C ABI; "kernels" lists all four
+  roofline     dominant kernel (dK/dV), timed alone with CUDA events through the C ABI, against
+               the measured peaks (burst tensor peak for such a short loop); "kernels" lists all four
   cpu_baseline fp32 eager oracle on the host cores, on a bounded sample of (b,h) slices
 --impl reference times that CPU oracle alone (the reference project's own CPU-runnable
 path is exactly this fp32 eager math; its Triton kernels need a GPU and the project
@@ -393,16 +393,23 @@ def main():
                     call()
                 t_ms = cuda_time_ms(call, iters)
                 nbytes = kernel_bytes(w, name)
-                t_roof = max(fl / (peaks["tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
+                # a kernel timed alone for a fraction of a second runs at the full SM clock: it is
+                # held against the burst tensor peak; only a loop long enough to reach the power
+                # cap is held against the sustained one
+                regime = "burst" if iters * t_ms < 250.0 else "sustained"
+                tpeak = peaks["tflops_burst"] if regime == "burst" else peaks["tflops"]
+                t_roof = max(fl / (tpeak * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
                 kernels[name] = {"ms": round(t_ms, 4), "tflops": round(fl / t_ms / 1e9, 1),
                                  "gbs": round(nbytes / t_ms / 1e6, 1), "roof_ms": round(t_roof, 4),
-                                 "frac": round(t_roof / t_ms, 3)}
+                                 "frac": round(t_roof / t_ms, 3), "tensor_peak": regime}
             kd = kernels["dkdv"]
-            tensor_bound = flops(w, "dkdv") / (peaks["tflops"] * 1e12) >= kernel_bytes(w, "dkdv") / (peaks["hbm_gbs"] * 1e9)
+            tpeak = peaks["tflops_burst"] if kd["tensor_peak"] == "burst" else peaks["tflops"]
+            tensor_bound = flops(w, "dkdv") / (tpeak * 1e12) >= kernel_bytes(w, "dkdv") / (peaks["hbm_gbs"] * 1e9)
             if tensor_bound:
                 roofline = {"kernel": "dkdv_kernel", "bound": "tensor", "achieved": kd["tflops"],
-                            "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(kd["tflops"] / peaks["tflops"], 3),
-                            "traffic": None, "peak_source": peaks["source"] + " sustained bf16"}
+                            "peak": tpeak, "unit": "TFLOP/s", "frac": round(kd["tflops"] / tpeak, 3),
+                            "traffic": None,
+                            "peak_source": peaks["source"] + " " + kd["tensor_peak"] + " bf16"}
             else:
                 roofline = {"kernel": "dkdv_kernel", "bound": "hbm", "achieved": kd["gbs"],
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kd["gbs"] / peaks["hbm_gbs"], 3),
