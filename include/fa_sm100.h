@@ -96,6 +96,13 @@ typedef struct fa_params {
 /* Library / ABI version (FA_ABI_VERSION of the build). */
 int fa_version(void);
 
+/*
+ * Number of attention kernels this library has launched since it was loaded (forward 1 per
+ * call; backward 3: preprocess, dK/dV, dQ).  For benchmarks and tests that must show the
+ * work ran here.  No counterpart in the reference.
+ */
+uint64_t fa_launch_count(void);
+
 /* Text for an fa_error code; never null. */
 const char* fa_status_string(int code);
 
@@ -130,7 +137,12 @@ int fa_bwd(const fa_params* p, void* stream);
  */
 int fa_bwd_static_scratch(const fa_params* p, void* stream);
 
-/* The three backward stages on their own (per-kernel timing and tests). */
+/*
+ * The three backward stages on their own (per-kernel timing and tests).  Order matters:
+ * fa_bwd_pre writes `delta`, which the other two read; and when write_dbias is 1 with a
+ * 16-bit bias, fa_bwd_dq READS `dbias` (it forms dQ from the dS tiles fa_bwd_dkdv has just
+ * stored there), so fa_bwd_dkdv must have run on the same stream before it.
+ */
 int fa_bwd_pre(const fa_params* p, void* stream);  /* _attn_bwd_preprocess FA:197-233 */
 int fa_bwd_dkdv(const fa_params* p, void* stream); /* _attn_bwd_dkdv       FA:330-454 */
 int fa_bwd_dq(const fa_params* p, void* stream);   /* _attn_bwd_dq         FA:538-646 */
@@ -143,8 +155,28 @@ int fa_bwd_dq(const fa_params* p, void* stream);   /* _attn_bwd_dq         FA:53
  */
 int fa_last_device_status(int device, int32_t out[8]);
 
-/* Clears the status word of `device` (synchronises the device). */
+/* Clears the status word of `device` and its host copy (synchronises the device). */
 int fa_reset_device_status(int device);
+
+/*
+ * Registers `host_words` (8 x int32 of page-locked host memory, e.g. from cudaHostAlloc;
+ * NULL to unregister) as a host copy of the status word of `device`: a kernel that abandons
+ * a wait writes words 0..5 there as well, so the host can notice the failure by reading
+ * host_words[0] before its next call, without synchronising.  The memory stays owned by
+ * the caller and must outlive the registration.  Synchronises the device once.  No
+ * counterpart in the reference (its kernels have no waits of their own).
+ */
+int fa_set_status_mirror(int device, int32_t* host_words);
+
+/*
+ * Failure-path self-test: launches one CTA that waits, for at most `limit_us`
+ * microseconds (1..100000), on a barrier nothing ever completes.  The wait gives up, the
+ * kernel returns, and the status word reads {1, kernel 101, block 0, 0, site 7, limit_us}.
+ * Every later kernel of the library on this device then does no work until
+ * fa_reset_device_status() is called.  Nothing hangs or faults.  No counterpart in the
+ * reference.
+ */
+int fa_selftest_wait_timeout(int device, uint32_t limit_us, void* stream);
 
 /*
  * Self-test of the tensor-core building blocks on one 128x128x128 tile:

@@ -20,7 +20,7 @@ def test_operators_are_registered_with_shape_only_implementations():
         assert lse.shape == (2, 3, 100) and lse.dtype == torch.float32
         dq, dk, dv, dbias = ops.attn_bwd(o, q, k, v, o, lse, bias, False, 0.125, True)
         assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
-        assert dbias.shape == bias.shape and dbias.stride(2) % 8 == 0  # 16-byte row pitch
+        assert dbias.shape == bias.shape and dbias.is_contiguous()  # dense, as the reference returns it
         assert ops.attn_bwd(o, q, k, v, o, lse, None, True, 0.125, False)[3].numel() == 0
 
 

@@ -78,3 +78,72 @@ def test_two_rank_gloo_run_reproduces_the_unsharded_result(B, H):
         p.join(120)
         assert p.exitcode == 0
     assert out_q.get(timeout=10) == 0.0
+
+
+# ---- the same on GPUs: real kernels, NCCL gather, bitwise comparison with the unsharded run
+
+def _gpu_worker(rank, world, port, B, H, M, N, D, causal, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from triton_flashattn_b200 import flash_attention_fn
+
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(5)  # every rank draws the same global problem
+    q, k, v, do = (torch.randn(B, s, H, D, generator=g).to(dt) for s in (M, N, N, M))
+    bias = (0.5 * torch.randn(B, H, M, N, generator=g)).to(dt)
+
+    def run(qs, ks, vs, bs, dos):
+        qs, ks, vs, bs = (t.contiguous().to(dev).requires_grad_() for t in (qs, ks, vs, bs))
+        out = flash_attention_fn(qs, ks, vs, bs, causal, None)
+        out.backward(dos.contiguous().to(dev))
+        return {"out": out.detach(), "dq": qs.grad, "dk": ks.grad, "dv": vs.grad, "dbias": bs.grad}
+
+    sh = shard_batch_heads(B, H, rank, world)
+    mine = run(sh.slice_bshd(q), sh.slice_bshd(k), sh.slice_bshd(v), sh.slice_bhmn(bias), sh.slice_bshd(do))
+    # the shard against the fp32 oracle, worst error over all ranks
+    ref = oracle.attention_backward(sh.slice_bshd(q).to(dev), sh.slice_bshd(k).to(dev), sh.slice_bshd(v).to(dev),
+                                    sh.slice_bhmn(bias).to(dev), causal, None, sh.slice_bshd(do).to(dev))
+    err = torch.tensor([max((mine[n].float() - ref[n].float()).abs().max().item() for n in mine)], device=dev)
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    bad = []
+    whole = run(q, k, v, bias, do) if rank == 0 else None
+    for name in ("out", "dq", "dk", "dv", "dbias"):
+        parts = [torch.empty_like(mine[name].contiguous()) for _ in range(world)]
+        dist.all_gather(parts, mine[name].contiguous())
+        if rank == 0:
+            for rr, part in enumerate(parts):
+                s2 = shard_batch_heads(B, H, rr, world)
+                full = s2.slice_bhmn(whole[name]) if name == "dbias" else s2.slice_bshd(whole[name])
+                if not torch.equal(full, part):
+                    bad.append(f"{name}@rank{rr}")
+    torch.cuda.synchronize()
+    if rank == 0:
+        out_q.put((err.item(), bad))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,H,causal", [(2, 4, True), (1, 4, False)])
+def test_two_gpu_shards_equal_the_unsharded_gpu_result_bitwise(B, H, causal):
+    """Two ranks, one GPU each, NCCL: every rank runs the CUDA kernels on its (batch, head)
+    shard, out/dq/dk/dv/dbias are all_gathered and rank 0 finds them bitwise equal to its own
+    unsharded run; the largest error against the fp32 oracle over all shards stays in tolerance."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_worker, args=(r, 2, port, B, H, 640, 512, 128, causal, out_q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    err, bad = out_q.get(timeout=10)
+    assert bad == [], f"shards differ from the unsharded run: {bad}"
+    assert err <= 4e-2, err  # bf16 tolerance plus the 16-bit rounding of large gradients

@@ -62,6 +62,7 @@ class FaParams(ctypes.Structure):
 
 EXPORTED_SYMBOLS = (
     "fa_version",
+    "fa_launch_count",
     "fa_status_string",
     "fa_fwd",
     "fa_bwd",
@@ -71,7 +72,9 @@ EXPORTED_SYMBOLS = (
     "fa_bwd_dq",
     "fa_last_device_status",
     "fa_reset_device_status",
+    "fa_set_status_mirror",
     "fa_selftest_umma",
+    "fa_selftest_wait_timeout",
 )
 
 _lib = None
@@ -95,6 +98,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(path)
     P = ctypes.POINTER(FaParams)
     lib.fa_version.restype = ctypes.c_int
+    lib.fa_launch_count.restype = ctypes.c_uint64
     lib.fa_status_string.restype = ctypes.c_char_p
     lib.fa_status_string.argtypes = [ctypes.c_int]
     for name in ("fa_fwd", "fa_bwd", "fa_bwd_static_scratch", "fa_bwd_pre", "fa_bwd_dkdv", "fa_bwd_dq"):
@@ -108,8 +112,42 @@ def load() -> ctypes.CDLL:
     lib.fa_selftest_umma.restype = ctypes.c_int
     lib.fa_selftest_umma.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    lib.fa_set_status_mirror.restype = ctypes.c_int
+    lib.fa_set_status_mirror.argtypes = [ctypes.c_int, ctypes.c_void_p]
+    lib.fa_selftest_wait_timeout.restype = ctypes.c_int
+    lib.fa_selftest_wait_timeout.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p]
     _lib = lib
     return lib
+
+
+# Per device: (pinned torch tensor kept alive, ctypes view of its 8 words).  A kernel that
+# abandons a bounded wait writes its record there, so every API call can check the health of
+# the device with one host memory read instead of a synchronisation.
+_mirrors: dict[int, tuple] = {}
+
+
+def health_words(device: int):
+    """ctypes int32[8] view of the host copy of `device`'s status word (registered on first use)."""
+    m = _mirrors.get(device)
+    if m is None:
+        import torch
+
+        t = torch.zeros(8, dtype=torch.int32).pin_memory()
+        check(load().fa_set_status_mirror(device, t.data_ptr()), "fa_set_status_mirror")
+        m = (t, (ctypes.c_int32 * 8).from_address(t.data_ptr()))
+        _mirrors[device] = m
+    return m[1]
+
+
+def raise_if_unhealthy(device: int) -> None:
+    """Raises when a kernel on `device` has abandoned a wait since the last reset: from then on
+    every kernel of the library returns without doing any work, so results would be garbage."""
+    w = health_words(device)
+    if w[0] != 0:
+        raise RuntimeError(
+            f"a kernel on cuda:{device} abandoned a bounded wait (kernel {w[1]}, block {w[2]}, "
+            f"site {w[4]}, iteration {w[5]}); later kernels do no work until "
+            "_cabi.reset_device_status() is called")
 
 
 def status_string(code: int) -> str:

@@ -10,6 +10,8 @@ namespace fa {
 // One status word per device that loads the library (file-scope device storage).
 __device__ int g_fa_status[8];
 
+std::atomic<uint64_t> g_kernel_launches{0};
+
 namespace {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -33,6 +35,7 @@ EncodeTiledFn get_encode_fn() {
 
 constexpr int kMaxDevices = 64;
 int* g_status_ptr[kMaxDevices];
+volatile int32_t* g_mirror_host[kMaxDevices];  // pinned host copies of the status words
 std::mutex g_status_mu;
 
 struct DeviceGuard {
@@ -148,6 +151,8 @@ extern "C" {
 
 int fa_version(void) { return FA_ABI_VERSION; }
 
+uint64_t fa_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
+
 const char* fa_status_string(int code) {
   switch (code) {
     case FA_OK: return "ok";
@@ -221,8 +226,37 @@ int fa_last_device_status(int device, int32_t out[8]) {
 int fa_reset_device_status(int device) {
   return with_device(device, [&](int* st) {
     if (cudaDeviceSynchronize() != cudaSuccess) return (int)FA_ERR_CUDA;
-    if (cudaMemset(st, 0, 8 * sizeof(int)) != cudaSuccess) return (int)FA_ERR_CUDA;
+    // words 6..7 (address of the host copy) stay
+    if (cudaMemset(st, 0, 6 * sizeof(int)) != cudaSuccess) return (int)FA_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_status_mu);
+    if (volatile int32_t* h = g_mirror_host[device])
+      for (int i = 0; i < 6; ++i) h[i] = 0;
     return (int)FA_OK;
+  });
+}
+
+int fa_set_status_mirror(int device, int32_t* host_words) {
+  return with_device(device, [&](int* st) {
+    unsigned long long dev_addr = 0;
+    if (host_words) {
+      void* d = nullptr;
+      if (cudaHostGetDevicePointer(&d, host_words, 0) != cudaSuccess) return (int)FA_ERR_CUDA;
+      dev_addr = reinterpret_cast<unsigned long long>(d);
+      for (int i = 0; i < 8; ++i) host_words[i] = 0;
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) return (int)FA_ERR_CUDA;
+    if (cudaMemcpy(st + 6, &dev_addr, sizeof(dev_addr), cudaMemcpyHostToDevice) != cudaSuccess)
+      return (int)FA_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_status_mu);
+    g_mirror_host[device] = host_words;
+    return (int)FA_OK;
+  });
+}
+
+int fa_selftest_wait_timeout(int device, uint32_t limit_us, void* stream) {
+  if (limit_us < 1 || limit_us > 100000) return FA_ERR_SHAPE;
+  return with_device(device, [&](int* st) {
+    return launch_selftest_timeout(limit_us, static_cast<cudaStream_t>(stream), st);
   });
 }
 

@@ -40,12 +40,6 @@
 #include "fa_host.cuh"
 
 namespace fa {
-#ifdef FA_TRACE
-__device__ long long g_fa_trace_dkdv[8192];
-#define TR(role, step, slot) do { if (blockIdx.x == 0 && (step) < 16) g_fa_trace_dkdv[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TR(role, step, slot) do {} while (0)
-#endif
 namespace {
 
 struct DkdvParams {
@@ -267,27 +261,23 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           if (gs >= 1) ok = mbar_wait_hot(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
           if (ok) ok = wait_polled(pq, &q_full[qs], q_par, ctx, kSiteQFull, t);
           if (!ok) break;
-          TR(1, gs, 1);
           tc_fence_after();
           const uint32_t pdo = mbar_poll(&do_full[ds], do_par);
           issue_gemm_ss<KS_D, false, false>(tmem + kColS, qs ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
                                             idesc_s, false);
           mma_commit(&s_full);
           mma_commit(&q_empty[qs]);
-          TR(1, gs, 2);
           // dP_gs: same for the dP columns; dO_gs replaces dO_{gs-1} after dV_{gs-1} when
           // single-staged
           if (gs >= 1) ok = mbar_wait_hot(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
           if (ok) ok = wait_polled(pdo, &do_full[ds], do_par, ctx, kSiteDoFull, t);
           if (!ok) break;
-          TR(1, gs, 3);
           tc_fence_after();
           issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ds ? do_km_1 : do_km_0, v_km, kBlk, kBlk,
                                             idesc_s, false);
           mma_commit(&dp_full);
           mma_commit(&do_empty[ds]);
           if (t == T_steps - 1) mma_commit(&kv_empty);  // K and V may be replaced
-          TR(1, gs, 4);
         }
         g += T_steps;
       }
@@ -348,13 +338,11 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           ok = mbar_wait_hot(&p_ready, gs & 1, ctx, kSitePReady, t);
           if (ok) ok = wait_polled(pdo, &do_full[ds], (gs / kDoStages) & 1, ctx, kSiteDoFull, t);
           if (!ok) break;
-          TR(2, gs, 1);
           tc_fence_after();
           issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
                                        t > 0);
           mma_commit(&do_empty[ds]);
           mma_commit(&dv_done);
-          TR(2, gs, 2);
           if (zeros_in_flight) {
             tma_store_wait_read<0>();
             mbar_arrive(&st_done);
@@ -364,13 +352,11 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           ok = mbar_wait_hot(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
           if (ok) ok = wait_polled(pq, &q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
           if (!ok) break;
-          TR(2, gs, 3);
           tc_fence_after();
           issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
                                        t > 0);
           mma_commit(&q_empty[qs]);
           mma_commit(&dk_done);
-          TR(2, gs, 4);
           if (stores_here) {
             const int m0 = (i_start + t) * 128;
             tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
@@ -442,8 +428,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
                           p.bias_vec32 != 0);
       }
       // -LSE2 / delta of the row; rows beyond M get -inf / 0, which makes their P and dS zero
-      lse_next = row_ok ? -__ldg(p.lse + (int64_t)bh_ * p.M + m) : -INFINITY;
-      delta_next = row_ok ? __ldg(p.delta + (int64_t)bh_ * p.M + m) : 0.f;
+      lse_next = row_ok ? -__ldcg(p.lse + (int64_t)bh_ * p.M + m) : -INFINITY;
+      delta_next = row_ok ? __ldcg(p.delta + (int64_t)bh_ * p.M + m) : 0.f;
     };
     // Loop state is kept small on purpose (registers): the running step count gs, the tile
     // counter it, and per tile bh, col0 and the current query block mb; the first query block
@@ -488,10 +474,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           ps = mbar_poll(&s_full, gs & 1);
 
         // ---- P
-        if (tid == 0) TR(0, gs, 0);
         ok = wait_warp_polled(ps, &s_full, gs & 1, ctx, kSiteSFull, t);
         if (!ok) break;
-        if (tid == 0) TR(0, gs, 1);
         tc_fence_after();
         float pr[32];
         tmem_ld32(tm_sc, reinterpret_cast<uint32_t*>(pr));
@@ -550,12 +534,10 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           for (int i = 0; i < 32; ++i)
             if (i >= limit) pr[i] = 0.f;
         }
-        if (tid == 0) TR(0, gs, 2);
         if (t >= 1) {
           ok = wait_warp_polled(pdv, &dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
           if (!ok) break;
         }
-        if (tid == 0) TR(0, gs, 3);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           sts128(sp_row + (((chunk0 + c) ^ (r & 7)) << 4), P2::pack(pr[c * 8 + 0], pr[c * 8 + 1]),
@@ -564,7 +546,6 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_ready);
-        if (tid == 0) TR(0, gs, 4);
 
         // ---- dS
         // dP, "dK of the previous step has read dS" and "its dbias store has": one combined look
@@ -583,7 +564,6 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           pdp = mbar_poll(&dp_full, gs & 1);
         ok = wait_warp_polled(pdp, &dp_full, gs & 1, ctx, kSiteDpFull, t);
         if (!ok) break;
-        if (tid == 0) TR(0, gs, 5);
         tc_fence_after();
         uint32_t dsu[16];
         // dP is fetched in two halves: fewer registers are live at once
@@ -606,17 +586,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
             dsu[hf * 8 + i] = P2::pack(f2_lo(d), f2_hi(d));
           }
         }
-        if (tid == 0) TR(0, gs, 6);
         if (t >= 1) {
           ok = wait_warp_polled(pdk, &dk_done, (gs - 1) & 1, ctx, kSiteDkDone, t);
           if (!ok) break;
         }
-        if (tid == 0) TR(0, gs, 7);
         if (st_wait) {
           ok = wait_warp_polled(pst, &st_done, st_par, ctx, kSiteStDone, t);
           if (!ok) break;
         }
-        if (tid == 0) TR(0, gs, 8);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           sts128(sp_row + (L::kDs - L::kP) + (((chunk0 + c) ^ (r & 7)) << 4), dsu[c * 4 + 0],
@@ -624,7 +601,6 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ds_ready);
-        if (tid == 0) TR(0, gs, 9);
       }
       if (!ok) break;
 
@@ -709,12 +685,6 @@ int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t str
 
 }  // namespace
 
-#ifdef FA_TRACE
-extern "C" int fa_debug_read_trace_dkdv(long long* out, int n) {
-  cudaDeviceSynchronize();
-  return cudaMemcpyFromSymbol(out, g_fa_trace_dkdv, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   DkdvParams kp;

@@ -264,8 +264,8 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
       const int m = m0 + r;
       const bool row_ok = m < p.M;
       const int64_t bias_row = b * p.bias_sB + h * p.bias_sH + (int64_t)m * p.bias_sM;
-      const float neg_lse = row_ok ? -__ldg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
-      const float delta_r = row_ok ? __ldg(p.delta + (int64_t)bh * p.M + m) : 0.f;
+      const float neg_lse = row_ok ? -__ldcg(p.lse + (int64_t)bh * p.M + m) : -INFINITY;
+      const float delta_r = row_ok ? __ldcg(p.delta + (int64_t)bh * p.M + m) : 0.f;
       BiasRegs<BIAS> bnext;
       if (BIAS != 0)
         load_bias_row<BIAS>(bnext, p.bias, bias_row, row_ok, qt * 32, p.N, p.bias_vec32 != 0);
@@ -560,14 +560,9 @@ int launch_bias(const DqParams& kp, int bias_kind, bool from_ds, dim3 grid, cuda
 
 int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   DqParams kp;
-  // When dS has just been written as dbias (same 16-bit dtype as q) the streamed
-  // GEMM variant is used; set FA_DQ_RECOMPUTE=1 in the environment to force the
-  // general kernel (used by the tests to cover both).
-  static const bool force_recompute = [] {
-    const char* e = getenv("FA_DQ_RECOMPUTE");
-    return e && e[0] == '1';
-  }();
-  const bool from_ds = p.write_dbias && p.bias_kind == FA_BIAS_SAME && !force_recompute;
+  // When dS has just been written as dbias (same 16-bit dtype as q) the streamed GEMM
+  // variant is used, otherwise the general kernel.
+  const bool from_ds = p.write_dbias && p.bias_kind == FA_BIAS_SAME;
   int r = make_tmap_bshd(&kp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
   if (r) return r;
   r = make_tmap_bshd(&kp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, from_ds ? 64 : 128);

@@ -32,8 +32,8 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const PreParams p) {
     const T* orow = reinterpret_cast<const T*>(p.o) + b * p.o_sB + (int64_t)m * p.o_sM + h * p.o_sH;
     const T* drow =
         reinterpret_cast<const T*>(p.d_o) + b * p.do_sB + (int64_t)m * p.do_sM + h * p.do_sH;
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(orow) + sub);
-    const uint4 g = __ldg(reinterpret_cast<const uint4*>(drow) + sub);
+    const uint4 a = __ldcg(reinterpret_cast<const uint4*>(orow) + sub);
+    const uint4 g = __ldcg(reinterpret_cast<const uint4*>(drow) + sub);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

@@ -24,7 +24,10 @@ namespace fa {
 // ----------------------------------------------------------------------------
 // status word layout (int[8] in global memory, owned by the host API)
 //   [0] error code (0 = ok), [1] kernel id, [2] blockIdx.x, [3] blockIdx.y,
-//   [4] wait site id, [5] loop iteration
+//   [4] wait site id, [5] loop iteration,
+//   [6..7] 64-bit device-visible address of a pinned host copy of words 0..5 (0 = none):
+//          the kernel that records an error also writes it there, so the host learns of it
+//          without synchronising
 // ----------------------------------------------------------------------------
 enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusTmemAlloc = 2 };
 
@@ -138,51 +141,41 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Per-CTA abort context.  `abort_flag` lives in shared memory and is set by the
 // first waiter whose limit expires; every other waiter polls it so that all
 // roles leave together.  `status` is the global status word.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
 struct WaitCtx {
   volatile int* abort_flag;  // shared
   int* status;               // global
   int kernel_id;
+  uint64_t limit_ns = kWaitLimitNs;
 };
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
-
 // Returns true when the phase completed, false when the kernel must bail out.
-#if defined(FA_TRACE) || defined(FA_WAITLOG_ON)
-static __device__ int g_fa_waitlog[1 + 64 * 6];  // lane 0 of each warp only
-static __device__ __noinline__ void waitlog(int site, int iter, int why) {
-  if (threadIdx.x & 31) return;
-  const int i = atomicAdd(&g_fa_waitlog[0], 1);
-  if (i < 64) {
-    int* e = &g_fa_waitlog[1 + i * 6];
-    e[0] = blockIdx.x; e[1] = threadIdx.x; e[2] = site; e[3] = iter; e[4] = why; e[5] = 0;
-  }
-}
-#define FA_WAITLOG(site, iter, why) waitlog(site, iter, why)
-#else
-#define FA_WAITLOG(site, iter, why) do {} while (0)
-#endif
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
                                             int site, int iter) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.abort_flag) { FA_WAITLOG(site, iter, 2); return false; }
+    if (*ctx.abort_flag) return false;
     if ((++spins & 63u) == 0) {
       if (*reinterpret_cast<volatile int*>(ctx.status) != 0) {
         *ctx.abort_flag = 1;
         return false;
       }
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        FA_WAITLOG(site, iter, 1);
+      if (global_timer_ns() - t0 > ctx.limit_ns) {
         *ctx.abort_flag = 1;
         if (atomicCAS(ctx.status, 0, kStatusWaitTimeout) == 0) {
-          ctx.status[1] = ctx.kernel_id;
-          ctx.status[2] = blockIdx.x;
-          ctx.status[3] = blockIdx.y;
-          ctx.status[4] = site;
-          ctx.status[5] = iter;
+          const int rec[6] = {kStatusWaitTimeout, ctx.kernel_id, (int)blockIdx.x, (int)blockIdx.y, site, iter};
+          for (int i = 1; i < 6; ++i) ctx.status[i] = rec[i];
           __threadfence();
+          // host copy, if one is registered (words 6..7 hold its address)
+          volatile int* host = reinterpret_cast<volatile int*>(
+              *reinterpret_cast<volatile unsigned long long*>(ctx.status + 6));
+          if (host != nullptr) {
+            for (int i = 5; i >= 0; --i) host[i] = rec[i];
+            __threadfence_system();
+          }
         }
         return false;
       }
@@ -638,9 +631,11 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// 32-byte (one full sector) read-only global load that bypasses L1.
+// 32-byte (one full sector) global load served from L2.  Not the non-coherent (.nc) path:
+// every kernel here may start while its predecessor in the stream still runs, and .nc is
+// only defined for data that nobody writes during the whole lifetime of the reading kernel.
 __device__ __forceinline__ void ldg256(const void* ptr, uint32_t* r) {
-  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+  asm volatile("ld.global.cg.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
                  "=r"(r[7])
                : "l"(ptr));
@@ -702,7 +697,7 @@ __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bi
     } else {
 #pragma unroll
       for (int c = 0; c < kWords / 4; ++c) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(rowp + (col0 * kElem) + c * 16));
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rowp + (col0 * kElem) + c * 16));
         br.w[c * 4 + 0] = v.x;
         br.w[c * 4 + 1] = v.y;
         br.w[c * 4 + 2] = v.z;
@@ -719,8 +714,8 @@ __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bi
     for (int k = 0; k < kPerWord; ++k) {
       const int col = col0 + i * kPerWord + k;
       if (col < N) {
-        const uint32_t e = BIAS == 1 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rowp) + col)
-                                     : (uint32_t)__ldg(rowp + col);
+        const uint32_t e = BIAS == 1 ? (uint32_t)__ldcg(reinterpret_cast<const uint16_t*>(rowp) + col)
+                                     : (uint32_t)__ldcg(rowp + col);
         word |= e << (8 * kElem * k);
       }
     }

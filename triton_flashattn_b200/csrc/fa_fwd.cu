@@ -31,12 +31,6 @@
 #include "fa_host.cuh"
 
 namespace fa {
-#ifdef FA_TRACE
-__device__ long long g_fa_trace[8192];
-#define TR(role, step, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 16) g_fa_trace[(role) * 2048 + (step) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TR(role, step, slot) do {} while (0)
-#endif
 namespace {
 
 struct FwdParams {
@@ -216,14 +210,12 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           if (ok && j == 0) ok = mbar_wait(&q_full, it & 1, ctx, kSiteQ, it);
           if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
           if (!ok) break;
-          TR(1, g, 1);
           tc_fence_after();
           issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc,
                                              st ? k_desc_1 : k_desc_0, kBlk, kBlk, idesc_qk, false);
           mma_commit(&s_full[st]);
           mma_commit(&k_empty[st]);
           if (j == nblk - 1) mma_commit(&q_empty);
-          TR(1, g, 2);
         }
         gj += nblk;
       }
@@ -249,13 +241,11 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           ok = mbar_wait_hot(&p_full, g & 1, ctx, kSitePFull, j);
           if (ok) ok = wait_polled(pv, &v_full[st], (g >> 1) & 1, ctx, kSiteVFull, j);
           if (!ok) break;
-          TR(1, g, 4);
           tc_fence_after();
           issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, st ? v_desc_1 : v_desc_0,
                                  kBlk, idesc_pv, j > 0);
           mma_commit(&v_empty[st]);
           mma_commit(&pv_done[st]);
-          TR(1, g, 5);
         }
         gj += nblk;
       }
@@ -313,7 +303,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       // bias unit of this step: 16-bit bias -> two per block (this quarter's half); mask -> one
       const uint32_t unit = BIAS == 1 ? 2 * g + (qt >> 1) : g;
       const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
-      if (tid == 0) TR(0, g, 0);
       // the scores and the bias unit of this step are usually there already: one combined
       // look at both barriers (their answers travel together), blocking waits only if not
       uint32_t ps = 1, pbias = 1;
@@ -323,12 +312,10 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         ps = mbar_poll(&s_full[st], (g >> 1) & 1);
       ok = wait_warp_polled(ps, &s_full[st], (g >> 1) & 1, ctx, kSiteSFull, j);
       if (!ok) break;
-      if (tid == 0) TR(0, g, 1);
       tc_fence_after();
       float s[32];
       tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 32), reinterpret_cast<uint32_t*>(s));
       tmem_ld_wait();
-      if (tid == 0) TR(0, g, 2);
       // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
       // Without a bias (and a positive scale) the raw q.k is kept and the scale is
       // folded into the exponent below.
@@ -387,7 +374,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         for (int i = 0; i < 32; ++i)
           if (i >= limit) s[i] = -INFINITY;
       }
-      if (tid == 0) TR(0, g, 3);
       // ---- row maximum over this quarter, exchanged with the three partner quarters
       float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
       float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
@@ -401,7 +387,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       mx0 = max3(mx0, s[28], s[29]);  // 12 + 2*8 = 28 consumed; 28..31 left
       mx1 = max3(mx1, s[30], s[31]);
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      if (tid == 0) TR(0, g, 4);
       xchg[gx & 1][qt][r] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(row_bar);
@@ -415,7 +400,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
       if (!ok) break;
       mx = fmaxf(fmaxf(xchg[gx & 1][0][r], xchg[gx & 1][1][r]),
                  fmaxf(xchg[gx & 1][2][r], xchg[gx & 1][3][r])) * mul;  // block maximum, log2 domain
-      if (tid == 0) TR(0, g, 5);
       const bool need = mx > m_used + 8.0f;
       const bool any_need = __any_sync(0xffffffffu, need);
       // O may only be touched once P_{j-1} V_{j-1} has completed.
@@ -423,7 +407,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         ok = wait_warp_polled(ppv, &pv_done[st ^ 1], ((g - 1) >> 1) & 1, ctx, kSitePvDone, j);
         if (!ok) break;
       }
-      if (tid == 0) TR(0, g, 6);
       if (any_need) {
         const float m_new = need ? mx : m_used;
         const float alpha = need ? ex2(m_used - m_new) : 1.0f;
@@ -439,7 +422,6 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
           tmem_st_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
         }
       }
-      if (tid == 0) TR(0, g, 7);
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       f32x2 sum01 = f2(0.f, 0.f), sum23 = f2(0.f, 0.f);
       const f32x2 mul2 = f2(mul, mul), negm2 = f2(neg_m, neg_m);
@@ -465,15 +447,12 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
         pk[i + 1] = P2::pack(p2, p3);
       }
       l += (f2_lo(sum01) + f2_hi(sum01)) + (f2_lo(sum23) + f2_hi(sum23));
-      if (tid == 0) TR(0, g, 8);
       // P (16 bit) over the S columns: this quarter's 32 keys -> 16 packed columns
       tmem_st16(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 16), pk);
       tmem_st_wait();
-      if (tid == 0) TR(0, g, 9);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-      if (tid == 0) TR(0, g, 10);
     }
     // ---- epilogue: O / l -> global, log-sum-exp
     if (!ok) break;
@@ -550,18 +529,6 @@ int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stre
 
 }  // namespace
 
-#if defined(FA_TRACE) || defined(FA_WAITLOG_ON)
-extern "C" int fa_debug_read_waitlog(int* out) {
-  cudaDeviceSynchronize();
-  return cudaMemcpyFromSymbol(out, g_fa_waitlog, sizeof(int) * (1 + 64 * 6)) == cudaSuccess ? 0 : 1;
-}
-#endif
-#ifdef FA_TRACE
-extern "C" int fa_debug_read_trace(long long* out, int n) {
-  cudaDeviceSynchronize();
-  return cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   FwdParams fp;

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/fa_sm100.h"
 
 namespace fa {
@@ -31,12 +33,16 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status);
 int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status);
 int launch_selftest(int mode, int dtype, const void* a, const void* b, void* c, cudaStream_t stream,
                     int* status);
+int launch_selftest_timeout(uint32_t limit_us, cudaStream_t stream, int* status);
 
 // Grid of a persistent kernel: one CTA per SM of the current device, never more than
 // there are work units.  The environment variable FA_MAX_CTAS (a positive integer, read at
 // every launch) lowers the cap; tests use it to make small problems walk many tiles
 // per CTA.
 int persistent_grid(int n_tiles);
+
+// Kernels launched by this library since it was loaded (all devices, all threads).
+extern std::atomic<uint64_t> g_kernel_launches;
 
 // Launch with the programmatic-stream-serialization attribute (see grid_dep_wait()).
 template <typename Kern, typename Params>
@@ -52,7 +58,9 @@ inline int launch_overlapped(Kern kern, dim3 grid, int threads, size_t smem, cud
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, params) == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, kern, params) != cudaSuccess) return FA_ERR_CUDA;
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  return FA_OK;
 }
 
 // Head dims are computed on a padded width: 16/32/64 -> 64, 128 -> 128.

@@ -140,7 +140,30 @@ __global__ void __launch_bounds__(128, 1) selftest_kernel(const __grid_constant_
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// One CTA whose threads all wait, with a limit the caller chooses, for a barrier phase that
+// nothing ever completes.  The wait gives up, the status word (and its host copy) records
+// kernel 101 / site 7, and the kernel returns: the failure path of every kernel of this
+// library, exercised without hanging or faulting anything.
+__global__ void __launch_bounds__(128, 1) selftest_timeout_kernel(int* status, uint32_t limit_us) {
+  __shared__ uint64_t never;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&never, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  WaitCtx ctx{&abort_flag, status, 101, static_cast<uint64_t>(limit_us) * 1000ull};
+  const bool live = *reinterpret_cast<volatile int*>(status) == 0;
+  if (live) (void)mbar_wait(&never, 0, ctx, 7, static_cast<int>(limit_us));
+}
+
 }  // namespace
+
+int launch_selftest_timeout(uint32_t limit_us, cudaStream_t stream, int* status) {
+  selftest_timeout_kernel<<<1, 128, 0, stream>>>(status, limit_us);
+  return cudaGetLastError() == cudaSuccess ? FA_OK : FA_ERR_CUDA;
+}
 
 int launch_selftest(int mode, int dtype, const void* a, const void* b, void* c, cudaStream_t stream,
                     int* status) {

@@ -105,6 +105,10 @@ def _check_inputs(q, k, v, bias):
     return B, M, N, H, D
 
 
+def _device_index(t: torch.Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
 def _params(q, k, v, o, lse, bias_t, bias_kind, causal, sm_scale):
     B, M, H, D = q.shape
     N = k.shape[1]
@@ -142,6 +146,7 @@ def _flash_attn_fwd(q, k, v, bias, causal, sm_scale):
     """Host launcher of the forward kernel; returns (o, lse2).  Mirrors FA:649-685.
     lse2 is the log2-domain log-sum-exp, fp32, laid out (B, H, M)."""
     B, M, N, H, D = _check_inputs(q, k, v, bias)
+    _cabi.raise_if_unhealthy(_device_index(q))
     q, k, v = _tile_ready(q), _tile_ready(k), _tile_ready(v)
     bias_t, kind = _classify_bias(bias, q)
     o = q.new_empty((B, M, H, D))
@@ -156,6 +161,7 @@ def _flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbi
     Mirrors FA:688-763.  dbias, when given, must be a (B, H, M, N) tensor in q's dtype
     whose row pitch is a multiple of 16 bytes (see `_empty_dbias`)."""
     B, M, N, H, D = _check_inputs(q, k, v, bias)
+    _cabi.raise_if_unhealthy(_device_index(q))
     q, k, v, o, do = (_tile_ready(t) for t in (q, k, v, o, do))
     bias_t, kind = _classify_bias(bias, q)
     delta = torch.empty((B, H, M), device=q.device, dtype=torch.float32)
@@ -172,13 +178,33 @@ def _flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbi
 
 
 def _empty_dbias(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    """Uninitialised (B, H, M, N) gradient buffer with a 16-byte aligned row pitch.
+    """Uninitialised (B, H, M, N) gradient buffer with a 16-byte aligned row pitch: dense
+    when N allows it, else a view of a padded buffer (the caller compacts it afterwards).
     No zero fill is needed: the dK/dV kernel writes every tile, including the
     causally skipped ones (the reference relies on zeros_like, FA:799)."""
     B, H, M, N = bias.shape
-    n_pad = (N + 15) // 16 * 16
+    per16 = 16 // dtype.itemsize
+    n_pad = (N + per16 - 1) // per16 * per16
     buf = torch.empty((B, H, M, n_pad), dtype=dtype, device=bias.device)
     return buf[..., :N]
+
+
+def _finish_dbias(dbias, bias):
+    """Gradient as the reference returns it (FA:799): dense, in the bias's own dtype."""
+    if dbias is None:
+        return None
+    if dbias.dtype != bias.dtype:
+        return dbias.to(bias.dtype)  # also compacts a padded buffer
+    return dbias if dbias.is_contiguous() else dbias.contiguous()
+
+
+def _grad_like(t: torch.Tensor) -> torch.Tensor:
+    """empty_like (strides preserved, as FA:796-798) when the kernels can write through those
+    strides, else a contiguous tensor."""
+    g = torch.empty_like(t)
+    s0, s1, s2, s3 = g.stride()
+    ok = s3 == 1 and s0 > 0 and s1 > 0 and s2 > 0 and (s0 | s1 | s2) % 8 == 0 and g.data_ptr() % 16 == 0
+    return g if ok else torch.empty(t.shape, dtype=t.dtype, device=t.device)
 
 
 class FlashAttentionFn(torch.autograd.Function):
@@ -203,14 +229,10 @@ class FlashAttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse, bias = ctx.saved_tensors
-        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        dq, dk, dv = _grad_like(q), _grad_like(k), _grad_like(v)
         dbias = _empty_dbias(bias, q.dtype) if ctx.is_bias_trainable else None
         _flash_attn_bwd(do, q, k, v, o, bias, ctx.causal, ctx.sm_scale, lse, dq, dk, dv, dbias)
-        if dbias is not None and dbias.dtype != bias.dtype:
-            dbias = dbias.to(bias.dtype)
-        return dq, dk, dv, dbias, None, None
+        return dq, dk, dv, _finish_dbias(dbias, bias), None, None
 
 
 class FlashAttentionQKVPackedFn(torch.autograd.Function):
@@ -238,15 +260,15 @@ class FlashAttentionQKVPackedFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         qkv, o, lse, bias = ctx.saved_tensors
-        dqkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=qkv.device)
+        dqkv = torch.empty_like(qkv)
+        if not dqkv.is_contiguous():
+            dqkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=qkv.device)
         dbias = _empty_dbias(bias, qkv.dtype) if ctx.is_bias_trainable else None
         _flash_attn_bwd(
             do, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, bias, ctx.causal, ctx.sm_scale, lse,
             dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2], dbias,
         )
-        if dbias is not None and dbias.dtype != bias.dtype:
-            dbias = dbias.to(bias.dtype)
-        return dqkv, dbias, None, None
+        return dqkv, _finish_dbias(dbias, bias), None, None
 
 
 def flash_attention_fn(q, k, v, bias=None, causal=False, sm_scale=None):

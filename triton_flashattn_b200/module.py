@@ -36,22 +36,15 @@ def _attn_fwd_fake(q, k, v, bias, causal, sm_scale):
     return q.new_empty((B, M, H, D)), q.new_empty((B, H, M), dtype=torch.float32)
 
 
-def _dbias_pitch(n: int) -> int:
-    return (n + 15) // 16 * 16
-
-
 @torch.library.custom_op(f"{_NS}::attn_bwd", mutates_args=(), device_types="cuda")
 def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
              lse: torch.Tensor, bias: Optional[torch.Tensor], causal: bool, sm_scale: float,
              need_dbias: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dq, dk, dv, dbias); dbias is an empty (0,) tensor unless `need_dbias`."""
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = _fa._grad_like(q), _fa._grad_like(k), _fa._grad_like(v)
     dbias = _fa._empty_dbias(bias, q.dtype) if need_dbias else None
     _fa._flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbias)
-    if dbias is None:
-        dbias = q.new_empty((0,))
-    elif dbias.dtype != bias.dtype:
-        dbias = dbias.to(bias.dtype)
+    dbias = q.new_empty((0,)) if dbias is None else _fa._finish_dbias(dbias, bias)
     return dq, dk, dv, dbias
 
 
@@ -60,11 +53,7 @@ def _attn_bwd_fake(do, q, k, v, o, lse, bias, causal, sm_scale, need_dbias):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     if not need_dbias:
         return dq, dk, dv, q.new_empty((0,))
-    B, H, M, N = bias.shape
-    if bias.dtype != q.dtype:  # converted copy: contiguous
-        return dq, dk, dv, bias.new_empty((B, H, M, N))
-    pitch = _dbias_pitch(N)
-    return dq, dk, dv, q.new_empty((B, H, M, pitch))[..., :N]
+    return dq, dk, dv, bias.new_empty(tuple(bias.shape))  # dense, in the bias's dtype
 
 
 def _setup_context(ctx, inputs, output):
