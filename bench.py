@@ -671,6 +671,11 @@ def time_kernels(w, q, k, v, bias, do, trainable, peaks, fa_mod, _cabi, use_capt
             for _ in range(3):
                 call()
             nbytes = kernel_bytes(w, name)
+            # a pause first: right after a long loop the GPU still sits at the clock its power
+            # cap forced, and a "short loop" number taken then is not a full-clock number
+            torch.cuda.synchronize()
+            time.sleep(1.0)
+            call()
             t_burst = cuda_time_ms(call, 20)
             t_long = cuda_time_ms(call, max(20, int(400.0 / max(t_burst, 1e-3))))
             roof_b = max(fl / (peaks["tflops_burst"] * 1e12), nbytes / hbm) * 1e3

@@ -1,28 +1,32 @@
 // Forward attention kernel for sm_100a.
 //
-// Persistent kernel, one CTA per SM.  A tile is 128 query rows of one (batch,
-// head); a CTA walks its tiles one after the other and, inside a tile, the key
-// blocks of 128 keys.  Ring stages, tensor-memory buffers and barrier phases run on
-// from tile to tile, so the next tile's Q / K / V / bias loads and its first
-// Q K^T product overlap the current tile's epilogue.  Roles (640 threads):
-//   warps 0-15 softmax: warp w owns query rows 32*(w&3)..+31 (= tensor-memory
-//              lanes) and the 32-key quarter (w>>2) of every block; the four
-//              quarters of a row exchange partial maxima through shared memory
-//   warp 16    TMA producer (one elected lane): Q per tile, K / V rings
-//   warp 17    MMA issuer for S = Q K^T (one lane), tensor-memory owner
-//   warp 18    MMA issuer for O += P V (one lane)
-//   warp 19    TMA producer of the bias / mask ring (one lane)
-// A barrier operation answers after ~200 cycles on this GPU; two issuers keep the
-// tensor pipe fed while one of them waits, and barriers are polled ahead of use.
-// Per key block j:  S_j = Q K_j^T (both operands in shared memory, accumulator
-// in tensor memory, double buffered) -> softmax threads read S_j, add the bias
-// tile (streamed by TMA into a shared-memory ring), apply masks, run the online
-// softmax in the log2 domain and write P_j (16 bit) back into tensor memory over
-// S_j -> O += P_j V_j with P as the tensor-memory operand and V MN-major in
-// shared memory.  S_{j+1} is issued before P_j V_j so the tensor core works
-// while the softmax of block j runs.  The running maximum is only raised when
-// it grows by more than 8 (log2 units); O in tensor memory is rescaled only
-// then.
+// Persistent kernel, one CTA per SM.  A CTA works on PAIRS of query tiles: two
+// consecutive blocks of 128 query rows of one (batch, head), which share every K / V
+// block they visit.  Roles (352 threads):
+//   warps 0-3   softmax group of tile 0: thread = one query row (= tensor-memory lane)
+//   warps 4-7   softmax group of tile 1
+//   warp 8      TMA producer (one lane): Q pair per unit, K ring (128-key stages), V ring
+//               (64-key half stages)
+//   warp 9      MMA issuer (one lane), tensor-memory owner
+//   warp 10     TMA producer of the bias / mask ring (one lane); it also asks for the
+//               tiles a few units ahead to be pulled into L2
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  Per key block j and tile t:
+//   S_t = Q_t K_j^T           (both operands in shared memory, N = 128)
+//   the row thread reads its 128 scores in two halves of 64 keys; per half it adds the
+//   bias tile (streamed by TMA into a ring of [128 rows][64 keys] units), applies the
+//   masks, updates the running maximum (log2 domain), forms P = exp2(s - m), and writes
+//   the 16-bit P half over the S columns it has already consumed
+//   O_t += P_t[half] V_j[half]   (P is the tensor-memory operand, V MN-major in shared
+//                                  memory), issued per half so that it overlaps the
+//                                  softmax of the other half
+// A row is owned by one thread, so the row maximum and the row sum need no exchange
+// between threads.  While one tile's softmax runs, the tensor core works on the other
+// tile: the issue order is PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1).  All tensor-core work is
+// issued by one thread; products issued by one thread execute in issue order, so
+// S_t(j+1) needs no barrier against PV_t(j), which reads P out of the same columns.
+// The running maximum is only raised when it grows by more than 8 (log2 units); only
+// then is O rescaled (by the row's own thread, after the products into it have finished).
+// Ring stages, tensor-memory buffers and barrier phases run on from unit to unit.
 //
 // Replaces _attn_fwd / _attn_fwd_inner of the reference (flash_attention.py
 // lines 12-194): same masks (bounds, top-left causal, bool, additive float
@@ -36,7 +40,7 @@ namespace {
 struct FwdParams {
   CUtensorMap map_q;
   CUtensorMap map_k;
-  CUtensorMap map_v;
+  CUtensorMap map_v;  // box of 64 keys
   CUtensorMap map_bias;
   void* o;
   float* lse;
@@ -45,71 +49,132 @@ struct FwdParams {
   int H, M, N, D;
   int causal;
   int bias_b_mul, bias_h_mul;
-  int n_mblk, n_tiles;  // query blocks per (batch, head); tiles = n_mblk * B * H
+  int n_mblk, n_pairs, n_units;  // query blocks / block pairs per (batch, head); units = pairs * B * H
   float sm_scale;
 };
 
-enum FwdSite { kSiteQ = 1, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty, kSiteSFull,
-               kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue, kSitePair, kSiteQEmpty, kSitePvDoneQK };
+enum FwdSite { kSiteQFull = 1, kSiteQEmpty, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty,
+               kSiteSFull, kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue };
 
 template <int DP, int BIAS>
 struct FwdSmem {
-  static constexpr int kTile = 128 * DP * 2;
-  // 16 KB bias units (one 64-key column half each); 3 at D=128 to stay inside 227 KB
-  static constexpr int kBiasStages = BIAS == 0 ? 0 : (DP == 128 ? 3 : 4);
+  static constexpr int kQTile = 128 * DP * 2;   // one query tile
+  static constexpr int kKStage = 128 * DP * 2;  // 128 keys
+  static constexpr int kVHalf = 64 * DP * 2;    // 64 keys
+  static constexpr int kKStages = 2;
+  static constexpr int kVStages = 3;
+  static constexpr int kBiasStages = BIAS == 0 ? 0 : 3;  // 16 KB units
   static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTile;
-  static constexpr int kV = kK + 2 * kTile;
-  static constexpr int kBias = kV + 2 * kTile;
+  static constexpr int kK = kQ + 2 * kQTile;
+  static constexpr int kV = kK + kKStages * kKStage;
+  static constexpr int kBias = kV + kVStages * kVHalf;
   static constexpr int kTotal = kBias + kBiasStages * kBlk;
   static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment
 };
 
+// The unit (pair of query tiles) number `it` of this CTA.  Units are numbered
+// (batch*head)-major; CTA c takes c, c+G, c+2G, ... so that CTAs running at the same time
+// share K / V in L2.  Causal: the entries of one (batch, head) are ordered [last, first,
+// last-1, first+1, ...] and a CTA takes two consecutive ones, a heavy and a light pair.
+struct Unit {
+  int bh, mb0;   // (batch, head) and first query block of the pair
+  int nb0, nb1;  // key blocks each tile visits (0: the tile does not exist)
+  int nmax;
+  __device__ __forceinline__ int nb(int t) const { return t ? nb1 : nb0; }
+};
+__device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
+  const int sh = p.causal ? 1 : 0;
+  const int c = static_cast<int>(blockIdx.x) + (it >> sh) * static_cast<int>(gridDim.x);
+  const int k = (c << sh) + (it & sh);
+  if (k >= p.n_units) return false;
+  u.bh = k / p.n_pairs;
+  const int pos = k - u.bh * p.n_pairs;
+  const int pair = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_pairs - 1 - (pos >> 1)) : pos;
+  u.mb0 = pair * 2;
+  const int nblk_all = (p.N + 127) >> 7;
+  u.nb0 = u.mb0 >= p.n_mblk ? 0 : (p.causal ? min(nblk_all, u.mb0 + 1) : nblk_all);
+  u.nb1 = u.mb0 + 1 >= p.n_mblk ? 0 : (p.causal ? min(nblk_all, u.mb0 + 2) : nblk_all);
+  u.nmax = max(u.nb0, u.nb1);
+  return true;
+}
+
+// Walks the bias units of this CTA in the order the softmax groups consume them:
+// per unit, per key block j, per tile t (if it visits j), per 64-key half (16-bit bias)
+// or once (byte mask, one [128][128] unit per block).
+template <int BIAS>
+struct BiasWalk {
+  int it = 0, j = 0, t = 0, h = 0;
+  Unit u;
+  bool valid = false;
+  __device__ __forceinline__ void settle(const FwdParams& p) {
+    // moves (it, j, t) forward to the next existing (tile, block), h stays 0
+    while (valid) {
+      if (j >= u.nmax) {
+        ++it;
+        j = 0;
+        t = 0;
+        valid = unit_at(p, it, u);
+        continue;
+      }
+      if (t >= 2) {
+        ++j;
+        t = 0;
+        continue;
+      }
+      if (j >= u.nb(t)) {
+        ++t;
+        continue;
+      }
+      return;
+    }
+  }
+  __device__ __forceinline__ void start(const FwdParams& p) {
+    valid = unit_at(p, 0, u);
+    settle(p);
+  }
+  __device__ __forceinline__ void next(const FwdParams& p) {
+    if (BIAS == 1 && h == 0) {
+      h = 1;
+      return;
+    }
+    h = 0;
+    ++t;
+    settle(p);
+  }
+  // coordinates of the current unit's box: (key, row, head, batch)
+  __device__ __forceinline__ void coords(const FwdParams& p, int& n0, int& m0, int& hh, int& bb) const {
+    const int b = u.bh / p.H;
+    n0 = j * 128 + h * 64;
+    m0 = (u.mb0 + t) * 128;
+    hh = (u.bh - b * p.H) * p.bias_h_mul;
+    bb = b * p.bias_b_mul;
+  }
+};
+
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
-  constexpr int KB = DP / 64;    // 64-column blocks per Q/K/V tile
-  constexpr int KS_QK = DP / 16; // MMA K slices of Q K^T
-  constexpr int kQD = DP / 4;    // output columns handled by one softmax thread (16 or 32)
+  constexpr int KB = DP / 64;     // 64-column blocks per Q / K / V tile
+  constexpr int KS_QK = DP / 16;  // MMA K slices of Q K^T
   constexpr uint32_t NB = L::kBiasStages > 0 ? L::kBiasStages : 1;
-  constexpr uint32_t kColS = 0, kColO = 256;
+  constexpr uint32_t VS = L::kVStages;
   constexpr uint32_t kTmemCols = 512;
+  constexpr int kVBlk = 64 * 128;  // bytes of one [64 keys][64] block of a V half stage
+  constexpr int kPf = 4;           // bias units asked into L2 ahead of the shared-memory ring
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
-      p_full, pv_done[2];
-  __shared__ uint64_t bias_full[4], bias_empty[4], row_bars[4];
-  __shared__ float xchg[2][4][128];  // [step parity][key quarter][row]: partial row maxima / sums
+  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[3], v_empty[3];
+  __shared__ uint64_t s_full[2], p_full[2][2], pv_done[2][2];
+  __shared__ uint64_t bias_full[3], bias_empty[3];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  // Persistent CTA: it walks tiles (tile = 128 query rows of one (batch, head)) and all
-  // roles keep running counters, so the rings, the tensor-memory buffers and every barrier
-  // phase carry on from one tile to the next: the loads and the first products of the next
-  // tile overlap the epilogue of the current one.
-  // Schedule: tiles are numbered (batch*head)-major; CTA c takes units c, c+G, c+2G, ...
-  // so that the CTAs running at the same time work on neighbouring tiles and share K / V in
-  // L2.  A unit is one tile, or - causal - two consecutive entries of the per-(batch, head)
-  // order [last, first, last-1, first+1, ...]: a heavy and a light block, so every unit
-  // carries about the same number of key blocks.
-  const int nblk_all = (p.N + 127) >> 7;
-  const int sched_sh = p.causal ? 1 : 0;
-  auto tile_at = [&](int it, int& bh, int& m_block, int& nblk) -> bool {
-    const int u = static_cast<int>(blockIdx.x) + (it >> sched_sh) * static_cast<int>(gridDim.x);
-    const int k = (u << sched_sh) + (it & sched_sh);
-    if (k >= p.n_tiles) return false;
-    bh = k / p.n_mblk;
-    const int pos = k - bh * p.n_mblk;
-    m_block = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_mblk - 1 - (pos >> 1)) : pos;
-    nblk = p.causal ? min(nblk_all, m_block + 1) : nblk_all;
-    return true;
-  };
 
   WaitCtx ctx{&abort_flag, p.status, 1};
 
@@ -120,21 +185,21 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      for (int h = 0; h < 2; ++h) {
+        mbar_init(&p_full[i][h], 4);
+        mbar_init(&pv_done[i][h], 1);
+      }
+    }
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-    }
-    mbar_init(&p_full, 16);
-    mbar_init(&pv_done[0], 1);
-    mbar_init(&pv_done[1], 1);
-    for (int i = 0; i < 4; ++i) {
       mbar_init(&bias_full[i], 1);
-      mbar_init(&bias_empty[i], BIAS == 2 ? 16 : 8);
-      mbar_init(&row_bars[i], 4);
+      mbar_init(&bias_empty[i], 4);
     }
     mbar_fence_init();
   }
-  if (warp == 17) {
+  if (warp == 9) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -142,363 +207,366 @@ __global__ void __launch_bounds__(640, 1) fwd_kernel(const __grid_constant__ Fwd
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  // A kernel launched after an earlier one recorded an error does no work.
   grid_dep_launch_next();
   grid_dep_wait();  // the previous kernel's results (and its status word) are visible from here
+  // A kernel launched after an earlier one recorded an error does no work.
   const bool live = *reinterpret_cast<volatile int*>(p.status) == 0;
 
-  if (warp == 16) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && live) {
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
       bool ok = true;
-      uint32_t gj = 0;  // key blocks issued so far, over all tiles
-      int bh, m_block, nblk;
-      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
-        const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
-        // the single Q tile is free once every Q K^T product of the previous tile is through
+      uint32_t gk = 0, gv = 0;  // key blocks / V halves issued so far, over all units
+      Unit u;
+      for (int it = 0; ok && unit_at(p, it, u); ++it) {
+        const int b = u.bh / p.H, h = u.bh - b * p.H;
+        // the Q pair is free once every Q K^T product of the previous unit is through
         if (it >= 1) ok = mbar_wait(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&q_full, L::kTile);
-        for (int kb = 0; kb < KB; ++kb)
-          tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &q_full, kb * 64, h, m0, b);
-        for (int j = 0; j < nblk && ok; ++j) {
-          const uint32_t g = gj + j;
-          const int st = g & 1;
+        mbar_expect_tx(&q_full, 2 * L::kQTile);
+        for (int t = 0; t < 2; ++t)
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_4d(smem + L::kQ + t * L::kQTile + kb * kBlk, &p.map_q, &q_full, kb * 64, h,
+                        (u.mb0 + t) * 128, b);
+        for (int j = 0; j < u.nmax && ok; ++j, ++gk) {
+          const int ks = gk & 1;
           const int n0 = j * 128;
-          if (g >= 2) ok = mbar_wait(&k_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+          if (gk >= 2) ok = mbar_wait(&k_empty[ks], ((gk >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
           if (!ok) break;
-          mbar_expect_tx(&k_full[st], L::kTile);
+          mbar_expect_tx(&k_full[ks], L::kKStage);
           for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64,
-                        h, n0, b);
-          if (g >= 2) ok = mbar_wait(&v_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
-          if (!ok) break;
-          mbar_expect_tx(&v_full[st], L::kTile);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64,
-                        h, n0, b);
+            tma_load_4d(smem + L::kK + ks * L::kKStage + kb * kBlk, &p.map_k, &k_full[ks], kb * 64, h,
+                        n0, b);
+          for (int hf = 0; hf < 2 && ok; ++hf, ++gv) {
+            const uint32_t vs = gv % VS, use = gv / VS;
+            if (use >= 1) ok = mbar_wait(&v_empty[vs], (use - 1) & 1, ctx, kSiteVEmpty, j);
+            if (!ok) break;
+            mbar_expect_tx(&v_full[vs], L::kVHalf);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kV + vs * L::kVHalf + kb * kVBlk, &p.map_v, &v_full[vs], kb * 64, h,
+                          n0 + hf * 64, b);
+          }
         }
-        gj += nblk;
       }
     }
-  } else if (warp == 17) {
-    // ------------------------------------------------------- MMA issuer: S = Q K^T
+  } else if (warp == 9) {
+    // --------------------------------------------------------------- MMA issuer
     if (lane == 0 && live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 128);
-      const uint32_t q_addr = smem_u32(smem + L::kQ);
-      const uint32_t k_addr = smem_u32(smem + L::kK);
-      const uint64_t q_desc = make_sdesc(q_addr, 0, 1024);
-      const uint64_t k_desc_0 = make_sdesc(k_addr, 0, 1024), k_desc_1 = make_sdesc(k_addr + L::kTile, 0, 1024);
-      bool ok = true;
-      uint32_t gj = 0;
-      int bh, m_block, nblk;
-      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
-        for (int j = 0; j < nblk && ok; ++j) {
-          const uint32_t g = gj + j;
-          const int st = g & 1;
-          const uint32_t pk = mbar_poll(&k_full[st], (g >> 1) & 1);
-          // S_g overwrites the columns that held P_{g-2}: P_{g-2} V_{g-2} must be through.
-          // One barrier per S buffer: its next completion (P_g V_g) needs this very S_g, so
-          // the barrier can never run two phases ahead of this wait, however long the issuer
-          // sat in another wait (a new tile's Q) in between.
-          if (g >= 2)
-            ok = mbar_wait_hot(&pv_done[st], ((g >> 1) - 1) & 1, ctx, kSitePvDoneQK, j);
-          if (ok && j == 0) ok = mbar_wait(&q_full, it & 1, ctx, kSiteQ, it);
-          if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
-          if (!ok) break;
-          tc_fence_after();
-          issue_gemm_ss<KS_QK, false, false>(tmem + kColS + st * 128, q_desc,
-                                             st ? k_desc_1 : k_desc_0, kBlk, kBlk, idesc_qk, false);
-          mma_commit(&s_full[st]);
-          mma_commit(&k_empty[st]);
-          if (j == nblk - 1) mma_commit(&q_empty);
-        }
-        gj += nblk;
-      }
-    }
-    __syncwarp();
-  } else if (warp == 18) {
-    // ------------------------------------------------------- MMA issuer: O += P V
-    if (lane == 0 && live) {
-      constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_pv = make_idesc(bf, false, true, 128, DP);
+      const uint32_t q_addr = smem_u32(smem + L::kQ), k_addr = smem_u32(smem + L::kK);
       const uint32_t v_addr = smem_u32(smem + L::kV);
-      const uint64_t v_desc_0 = make_sdesc(v_addr, kBlk, 1024), v_desc_1 = make_sdesc(v_addr + L::kTile, kBlk, 1024);
       bool ok = true;
-      uint32_t gj = 0;
-      int bh, m_block, nblk;
-      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
-        for (int j = 0; j < nblk && ok; ++j) {
-          const uint32_t g = gj + j;
-          const int st = g & 1;
-          const uint32_t pv = mbar_poll(&v_full[st], (g >> 1) & 1);
-          // P_g of a new tile is only announced after all sixteen softmax warps have read
-          // the previous tile's O, so the first product of a tile may overwrite it
-          ok = mbar_wait_hot(&p_full, g & 1, ctx, kSitePFull, j);
-          if (ok) ok = wait_polled(pv, &v_full[st], (g >> 1) & 1, ctx, kSiteVFull, j);
-          if (!ok) break;
-          tc_fence_after();
-          issue_gemm_ts<8, true>(tmem + kColO, tmem + kColS + st * 128, st ? v_desc_1 : v_desc_0,
-                                 kBlk, idesc_pv, j > 0);
-          mma_commit(&v_empty[st]);
-          mma_commit(&pv_done[st]);
-        }
-        gj += nblk;
-      }
-    }
-    __syncwarp();
-  } else if (warp == 19) {
-    // ------------------------------------------------------------ bias producer
-    // Its own thread: the bias ring is the HBM-latency-critical stream and must not
-    // queue behind the K / V ring's waits.
-    if (BIAS != 0 && lane == 0 && live) {
-      tma_prefetch_desc(&p.map_bias);
-      const uint64_t pol_stream = policy_evict_first();
-      uint32_t unit = 0;
-      bool ok = true;
-      int bh, m_block, nblk;
-      for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
-        const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
-        for (int j = 0; j < nblk && ok; ++j) {
-          const int n0 = j * 128;
-          // 16 KB units: 16-bit bias -> one per 64-key column half ([128 rows][64 keys]);
-          // byte mask -> one per block ([128 rows][128 keys]) shared by both halves
-          constexpr int kUnits = BIAS == 1 ? 2 : 1;
-          for (int u = 0; u < kUnits && ok; ++u, ++unit) {
-            const int bs = unit % NB;
-            const uint32_t use = unit / NB;
-            if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, j);
-            if (!ok) break;
-            mbar_expect_tx(&bias_full[bs], kBlk);
-            tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs],
-                             n0 + u * 64, m0, h * p.bias_h_mul, b * p.bias_b_mul, pol_stream);
-          }
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------- softmax
-    // thread = (query row r, key quarter qt): 32 of the 128 scores of the row per block
-    const int r = (warp & 3) * 32 + lane;
-    const int qt = warp >> 2;
-    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
-    uint64_t* row_bar = &row_bars[warp & 3];  // shared by the four warps that own the same rows
-    bool ok = live;
-    const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
-    const float scale_log2 = p.sm_scale * kLog2e;
-    uint32_t gj = 0;  // key blocks done so far, over all tiles (ring stages and barrier phases)
-    int bh, m_block, nblk;
-    for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
-    const int m0 = m_block * 128;
-    float m_used = -INFINITY;  // running maximum, log2 domain
-    float l = 0.f;             // partial row sum over this thread's keys
-    for (int j = 0; j < nblk && ok; ++j) {
-      const uint32_t g = gj + j;
-      const int st = g & 1;
-      const uint32_t gx = g + it;  // quarter exchanges so far: one per block, one per tile
-      // bias unit of this step: 16-bit bias -> two per block (this quarter's half); mask -> one
-      const uint32_t unit = BIAS == 1 ? 2 * g + (qt >> 1) : g;
-      const int n0 = j * 128 + qt * 32;  // first key of this thread's quarter
-      // the scores and the bias unit of this step are usually there already: one combined
-      // look at both barriers (their answers travel together), blocking waits only if not
-      uint32_t ps = 1, pbias = 1;
-      if (BIAS != 0)
-        mbar_poll2(&s_full[st], (g >> 1) & 1, &bias_full[unit % NB], (unit / NB) & 1, ps, pbias);
-      else
-        ps = mbar_poll(&s_full[st], (g >> 1) & 1);
-      ok = wait_warp_polled(ps, &s_full[st], (g >> 1) & 1, ctx, kSiteSFull, j);
-      if (!ok) break;
-      tc_fence_after();
-      float s[32];
-      tmem_ld32(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 32), reinterpret_cast<uint32_t*>(s));
-      tmem_ld_wait();
-      // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
-      // Without a bias (and a positive scale) the raw q.k is kept and the scale is
-      // folded into the exponent below.
-      float mul = kLog2e;  // exponent = s * mul - m
-      if (BIAS == 0) {
-        if (fold_scale) {
-          mul = scale_log2;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] *= p.sm_scale;
-        }
-      } else {
-        const int bs = unit % NB;
-        ok = wait_warp_polled(pbias, &bias_full[bs], (unit / NB) & 1, ctx, kSiteBiasFull, j);
+      uint32_t cs[2] = {0, 0};  // steps done per tile slot, over all units
+      uint32_t gk = 0, gv = 0;  // key blocks / V halves consumed before this unit
+      Unit u;
+      auto issue_qk = [&](int t, uint32_t kslot) {
+        issue_gemm_ss<KS_QK, false, false>(tmem + t * 128, make_sdesc(q_addr + t * L::kQTile, 0, 1024),
+                                           make_sdesc(k_addr + kslot * L::kKStage, 0, 1024), kBlk, kBlk,
+                                           idesc_qk, false);
+        mma_commit(&s_full[t]);
+      };
+      for (int it = 0; ok && unit_at(p, it, u); ++it) {
+        if (u.nmax == 0) continue;
+        // ---- first scores of both tiles
+        ok = mbar_wait(&q_full, it & 1, ctx, kSiteQFull, it);
+        if (ok) ok = mbar_wait(&k_full[gk & 1], (gk >> 1) & 1, ctx, kSiteKFull, 0);
         if (!ok) break;
-        const uint8_t* tile = smem + L::kBias + bs * kBlk;
-        if (BIAS == 1) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, (qt & 1) * 4 + c));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = P2::unpack(w[e]);
-              const int i = c * 8 + e * 2;
-              const f32x2 t = ffma2(f2(s[i], s[i + 1]), f2(p.sm_scale, p.sm_scale), f2(f.x, f.y));
-              s[i] = f2_lo(t);
-              s[i + 1] = f2_hi(t);
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (u.nb(t) > 0) issue_qk(t, gk & 1);
+        mma_commit(&k_empty[gk & 1]);
+        if (u.nmax == 1) mma_commit(&q_empty);
+        for (int j = 0; j < u.nmax && ok; ++j) {
+          const uint32_t kn = (gk + j + 1) & 1, kn_par = ((gk + j + 1) >> 1) & 1;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j >= u.nb(t)) continue;
+            const bool last_user = t == 1 || j >= u.nb1;  // tile 1 comes second when it visits j
+            // looked at early: the answers arrive while this thread waits for P
+            uint32_t pk = 1;
+            if (j + 1 < u.nb(t)) pk = mbar_poll(&k_full[kn], kn_par);
+            for (int h = 0; h < 2 && ok; ++h) {
+              const uint32_t gh = gv + 2 * j + h;
+              const uint32_t vs = gh % VS, v_par = (gh / VS) & 1;
+              const uint32_t pv = mbar_poll(&v_full[vs], v_par);
+              ok = mbar_wait_hot(&p_full[t][h], cs[t] & 1, ctx, kSitePFull, j);
+              if (ok) ok = wait_polled(pv, &v_full[vs], v_par, ctx, kSiteVFull, j);
+              if (!ok) break;
+              tc_fence_after();
+              issue_gemm_ts<4, true>(tmem + 256 + t * 128, tmem + t * 128 + h * 32,
+                                     make_sdesc(v_addr + vs * L::kVHalf, kVBlk, 1024), kVBlk, idesc_pv,
+                                     j > 0 || h > 0);
+              mma_commit(&pv_done[t][h]);
+              if (last_user) mma_commit(&v_empty[vs]);
             }
-          }
-        } else {
-          // byte mask tile: [128 rows][128 bytes]; this quarter reads chunks 2*qt, 2*qt+1
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4*>(tile + swz_off(r, qt * 2 + c));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const int i = c * 16 + e * 4 + k;
-                const bool keep = ((w[e] >> (8 * k)) & 0xFFu) != 0;
-                s[i] = keep ? s[i] * p.sm_scale : -INFINITY;
+            if (!ok) break;
+            ++cs[t];
+            if (j + 1 < u.nb(t)) {
+              // S_t(j+1) goes over the columns P_t(j) is read from: same issuing thread, so it
+              // executes after the products just issued
+              ok = wait_polled(pk, &k_full[kn], kn_par, ctx, kSiteKFull, j + 1);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(t, kn);
+              if (t == 1 || j + 1 >= u.nb1) {
+                mma_commit(&k_empty[kn]);
+                if (j + 2 >= u.nmax) mma_commit(&q_empty);
               }
             }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bias_empty[bs]);
+        gk += u.nmax;
+        gv += 2 * u.nmax;
       }
-      // ---- bounds and causal masks (only on blocks that need them)
-      if ((n0 + 32 > p.N) || (p.causal && n0 + 31 > m0)) {
-        int limit = p.N - n0;
-        if (p.causal) limit = min(limit, m0 + r - n0 + 1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= limit) s[i] = -INFINITY;
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ bias producer
+    if (BIAS != 0 && lane == 0 && live) {
+      tma_prefetch_desc(&p.map_bias);
+      const uint64_t pol_stream = policy_evict_first();
+      BiasWalk<BIAS> cur, ahead;
+      cur.start(p);
+      ahead.start(p);
+      auto l2 = [&](const BiasWalk<BIAS>& wk) {
+        int n0, m0, hh, bb;
+        wk.coords(p, n0, m0, hh, bb);
+        if (n0 < p.N) tma_prefetch_l2_4d(&p.map_bias, n0, m0, hh, bb);
+      };
+      for (int i = 0; i < kPf && ahead.valid; ++i) {
+        l2(ahead);
+        ahead.next(p);
       }
-      // ---- row maximum over this quarter, exchanged with the three partner quarters
-      float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
-      float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-      for (int i = 12; i + 7 < 32; i += 8) {
-        mx0 = max3(mx0, s[i], s[i + 1]);
-        mx1 = max3(mx1, s[i + 2], s[i + 3]);
-        mx2 = max3(mx2, s[i + 4], s[i + 5]);
-        mx3 = max3(mx3, s[i + 6], s[i + 7]);
-      }
-      mx0 = max3(mx0, s[28], s[29]);  // 12 + 2*8 = 28 consumed; 28..31 left
-      mx1 = max3(mx1, s[30], s[31]);
-      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      xchg[gx & 1][qt][r] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(row_bar);
-      // the exchange barrier and "P_{j-1} V_{j-1} is through" are looked at together
-      uint32_t prow = 0, ppv = 1;
-      if (j > 0)
-        mbar_poll2(row_bar, gx & 1, &pv_done[st ^ 1], ((g - 1) >> 1) & 1, prow, ppv);
-      else
-        prow = mbar_poll(row_bar, gx & 1);
-      ok = wait_warp_polled(prow, row_bar, gx & 1, ctx, kSitePair, j);
-      if (!ok) break;
-      mx = fmaxf(fmaxf(xchg[gx & 1][0][r], xchg[gx & 1][1][r]),
-                 fmaxf(xchg[gx & 1][2][r], xchg[gx & 1][3][r])) * mul;  // block maximum, log2 domain
-      const bool need = mx > m_used + 8.0f;
-      const bool any_need = __any_sync(0xffffffffu, need);
-      // O may only be touched once P_{j-1} V_{j-1} has completed.
-      if (j > 0) {
-        ok = wait_warp_polled(ppv, &pv_done[st ^ 1], ((g - 1) >> 1) & 1, ctx, kSitePvDone, j);
+      bool ok = true;
+      for (uint32_t unit = 0; ok && cur.valid; ++unit) {
+        if (ahead.valid) {
+          l2(ahead);
+          ahead.next(p);
+        }
+        const uint32_t bs = unit % NB, use = unit / NB;
+        if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, cur.j);
         if (!ok) break;
+        int n0, m0, hh, bb;
+        cur.coords(p, n0, m0, hh, bb);
+        mbar_expect_tx(&bias_full[bs], kBlk);
+        tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs], n0, m0, hh, bb,
+                         pol_stream);
+        cur.next(p);
       }
-      if (any_need) {
-        const float m_new = need ? mx : m_used;
-        const float alpha = need ? ex2(m_used - m_new) : 1.0f;
-        l *= alpha;
-        m_used = m_new;
-        if (j > 0) {
+    }
+  } else {
+    // ------------------------------------------------------------------- softmax
+    const int t = warp >> 2;                 // tile slot of this group
+    const int r = (warp & 3) * 32 + lane;    // query row inside the tile = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    const uint32_t tm_s = tmem_addr(tmem, lane_base, t * 128);
+    const uint32_t tm_o = tmem_addr(tmem, lane_base, 256 + t * 128);
+    constexpr int kU = BIAS == 1 ? 2 : 1;    // bias units per (tile, key block)
+    bool ok = live;
+    const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
+    const float scale_log2 = p.sm_scale * kLog2e;
+    uint32_t cs = 0;  // steps done by this tile slot, over all units
+    uint32_t bu = 0;  // bias units before the current key block, over all units and both tiles
+    Unit u;
+    for (int it = 0; ok && unit_at(p, it, u); ++it) {
+      const int nblk = u.nb(t);
+      const int m0 = (u.mb0 + t) * 128;
+      float m_used = -INFINITY;  // running maximum, log2 domain
+      float l = 0.f;             // row sum
+      for (int j = 0; j < u.nmax && ok; ++j) {
+        const int both = (j < u.nb0 ? 1 : 0) + (j < u.nb1 ? 1 : 0);
+        if (j < nblk) {
+          const uint32_t first = bu + ((t == 1 && j < u.nb0) ? kU : 0);
+          ok = wait_warp(&s_full[t], cs & 1, ctx, kSiteSFull, j);
+          if (!ok) break;
           tc_fence_after();
-          uint32_t o[kQD];
-          tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
-          tmem_ld_wait();
+#pragma unroll 1
+          for (int h = 0; h < 2 && ok; ++h) {
+            const uint32_t unit = BIAS == 1 ? first + h : first;
+            const uint32_t bs = unit % NB, b_par = (unit / NB) & 1;
+            uint32_t pbias = 1;
+            if (BIAS != 0 && (BIAS == 1 || h == 0)) pbias = mbar_poll(&bias_full[bs], b_par);
+            float s[64];
+            tmem_ld32(tm_s + h * 64, reinterpret_cast<uint32_t*>(s));
+            tmem_ld32(tm_s + h * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+            tmem_ld_wait();
+            const int n0 = j * 128 + h * 64;  // first key of this half
+            // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
+            // Without a bias (and a positive scale) the raw q.k is kept and the scale is
+            // folded into the exponent below.
+            float mul = kLog2e;  // exponent = s * mul - m
+            if (BIAS == 0) {
+              if (fold_scale) {
+                mul = scale_log2;
+              } else {
 #pragma unroll
-          for (int i = 0; i < kQD; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
-        }
-      }
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      f32x2 sum01 = f2(0.f, 0.f), sum23 = f2(0.f, 0.f);
-      const f32x2 mul2 = f2(mul, mul), negm2 = f2(neg_m, neg_m);
-      uint32_t pk[16];
+                for (int i = 0; i < 64; ++i) s[i] *= p.sm_scale;
+              }
+            } else {
+              if (BIAS == 1 || h == 0) {
+                ok = wait_warp_polled(pbias, &bias_full[bs], b_par, ctx, kSiteBiasFull, j);
+                if (!ok) break;
+              }
+              const uint32_t row = smem_u32(smem + L::kBias + bs * kBlk) + static_cast<uint32_t>(r) * 128u;
+              if (BIAS == 1) {
+                const f32x2 sc2 = f2(p.sm_scale, p.sm_scale);
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const f32x2 a01 = ffma2(f2(s[2 * i], s[2 * i + 1]), mul2, negm2);
-        const f32x2 a23 = ffma2(f2(s[2 * i + 2], s[2 * i + 3]), mul2, negm2);
-        // a quarter of the exponentials on the FMA pipe, the rest on the special-function unit
-        const float p0 = ex2(f2_lo(a01)), p1 = ex2(f2_hi(a01));
-        float p2, p3;
-        if ((i & 2) != 0) {
-          const f32x2 e23 = ex2_poly2(a23);
-          p2 = f2_lo(e23);
-          p3 = f2_hi(e23);
-        } else {
-          p2 = ex2(f2_lo(a23));
-          p3 = ex2(f2_hi(a23));
+                for (int c = 0; c < 8; ++c) {
+                  const uint4 v = lds128(row + (static_cast<uint32_t>(c ^ (r & 7)) << 4));
+                  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = P2::unpack(w[e]);
+                    const int i = c * 8 + e * 2;
+                    const f32x2 x = ffma2(f2(s[i], s[i + 1]), sc2, f2(f.x, f.y));
+                    s[i] = f2_lo(x);
+                    s[i + 1] = f2_hi(x);
+                  }
+                }
+              } else {
+                // byte mask unit: [128 rows][128 bytes]; this half reads chunks 4h .. 4h+3
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const uint4 v = lds128(row + (static_cast<uint32_t>((h * 4 + c) ^ (r & 7)) << 4));
+                  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                      const int i = c * 16 + e * 4 + k;
+                      const bool keep = ((w[e] >> (8 * k)) & 0xFFu) != 0;
+                      s[i] = keep ? s[i] * p.sm_scale : -INFINITY;
+                    }
+                  }
+                }
+              }
+              if (BIAS == 1 || h == 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bias_empty[bs]);
+              }
+            }
+            // ---- bounds and causal masks (only on halves that need them)
+            if ((n0 + 64 > p.N) || (p.causal && n0 + 63 > m0)) {
+              int limit = p.N - n0;
+              if (p.causal) limit = min(limit, m0 + r - n0 + 1);
+#pragma unroll
+              for (int i = 0; i < 64; ++i)
+                if (i >= limit) s[i] = -INFINITY;
+            }
+            // ---- row maximum of this half
+            float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+            float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+            for (int i = 12; i + 7 < 64; i += 8) {
+              mx0 = max3(mx0, s[i], s[i + 1]);
+              mx1 = max3(mx1, s[i + 2], s[i + 3]);
+              mx2 = max3(mx2, s[i + 4], s[i + 5]);
+              mx3 = max3(mx3, s[i + 6], s[i + 7]);
+            }
+            mx0 = max3(mx0, s[60], s[61]);  // 12 + 6*8 = 60 consumed; 60..63 left
+            mx1 = max3(mx1, s[62], s[63]);
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * mul;  // log2 domain
+            const bool need = mx > m_used + 8.0f;
+            if (__any_sync(0xffffffffu, need)) {
+              const float m_new = need ? mx : m_used;
+              const float alpha = need ? ex2(m_used - m_new) : 1.0f;
+              l *= alpha;
+              m_used = m_new;
+              if (j > 0 || h > 0) {
+                // O may only be touched once every product into it has finished: the last one
+                // issued is P V of the previous half
+                ok = h == 1 ? wait_warp(&pv_done[t][0], cs & 1, ctx, kSitePvDone, j)
+                            : wait_warp(&pv_done[t][1], (cs - 1) & 1, ctx, kSitePvDone, j);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < DP / 32; ++c) {
+                  uint32_t o[32];
+                  tmem_ld32(tm_o + c * 32, o);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                  tmem_st32(tm_o + c * 32, o);
+                }
+              }
+            }
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            f32x2 sum01 = f2(0.f, 0.f), sum23 = f2(0.f, 0.f);
+            const f32x2 mul2 = f2(mul, mul), negm2 = f2(neg_m, neg_m);
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const f32x2 a01 = ffma2(f2(s[2 * i], s[2 * i + 1]), mul2, negm2);
+              const f32x2 a23 = ffma2(f2(s[2 * i + 2], s[2 * i + 3]), mul2, negm2);
+              // a quarter of the exponentials on the FMA pipe, the rest on the special-function unit
+              const float p0 = ex2(f2_lo(a01)), p1 = ex2(f2_hi(a01));
+              float p2, p3;
+              if ((i & 2) != 0) {
+                const f32x2 e23 = ex2_poly2(a23);
+                p2 = f2_lo(e23);
+                p3 = f2_hi(e23);
+              } else {
+                p2 = ex2(f2_lo(a23));
+                p3 = ex2(f2_hi(a23));
+              }
+              sum01 = fadd2(sum01, f2(p0, p1));
+              sum23 = fadd2(sum23, f2(p2, p3));
+              pk[i] = P2::pack(p0, p1);
+              pk[i + 1] = P2::pack(p2, p3);
+            }
+            l += (f2_lo(sum01) + f2_hi(sum01)) + (f2_lo(sum23) + f2_hi(sum23));
+            // P (16 bit) over S columns this thread has already read: 64 keys -> 32 columns
+            tmem_st32(tm_s + h * 32, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[t][h]);
+          }
+          if (!ok) break;
+          ++cs;
         }
-        sum01 = fadd2(sum01, f2(p0, p1));
-        sum23 = fadd2(sum23, f2(p2, p3));
-        pk[i] = P2::pack(p0, p1);
-        pk[i + 1] = P2::pack(p2, p3);
+        bu += both * kU;
       }
-      l += (f2_lo(sum01) + f2_hi(sum01)) + (f2_lo(sum23) + f2_hi(sum23));
-      // P (16 bit) over the S columns: this quarter's 32 keys -> 16 packed columns
-      tmem_st16(tmem_addr(tmem, lane_base, kColS + st * 128 + qt * 16), pk);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
-    }
-    // ---- epilogue: O / l -> global, log-sum-exp
-    if (!ok) break;
-    gj += nblk;
-    ok = wait_warp(&pv_done[(gj - 1) & 1], ((gj - 1) >> 1) & 1, ctx, kSiteEpilogue, nblk);
-    // full row sum = sum of the four quarters
-    const uint32_t gx = gj + it;
-    if (ok) {
-      xchg[gx & 1][qt][r] = l;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(row_bar);
-      ok = wait_warp(row_bar, gx & 1, ctx, kSitePair, nblk);
-    }
-    if (ok) {
-      l = (xchg[gx & 1][0][r] + xchg[gx & 1][1][r]) + (xchg[gx & 1][2][r] + xchg[gx & 1][3][r]);
+      if (!ok) break;
+      if (nblk == 0) continue;
+      // ---- epilogue: O / l -> global, log-sum-exp
+      ok = wait_warp(&pv_done[t][1], (cs - 1) & 1, ctx, kSiteEpilogue, nblk);
+      if (!ok) break;
       tc_fence_after();
       const int m = m0 + r;
-      const int b = bh / p.H, h = bh - b * p.H;
+      const int b = u.bh / p.H, hd = u.bh - b * p.H;
       // a row whose keys are all masked out keeps m_used = -inf: output 0, LSE +inf (its
       // polynomial exponentials are 1e-38, not 0, so l alone does not tell)
       const bool any_key = m_used != -INFINITY && l > 0.f;
       const float inv = any_key ? 1.0f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM +
-                h * p.o_sH;
-      uint32_t o[kQD];
-      tmem_ld_cols<kQD>(tmem_addr(tmem, lane_base, kColO + qt * kQD), o);
-      tmem_ld_wait();
-      // O is in registers: the next tile's first P V product may overwrite it (it is issued
-      // after all sixteen warps have announced that tile's first P)
-      tc_fence_before();
-      if (m < p.M) {
+      T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sB + static_cast<int64_t>(m) * p.o_sM + hd * p.o_sH;
 #pragma unroll
-        for (int c = 0; c < kQD / 8; ++c) {
-          const int d = qt * kQD + c * 8;
-          if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + c * 8, inv);
+      for (int c = 0; c < DP / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tm_o + c * 32, o);
+        tmem_ld_wait();
+        if (m < p.M) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int d = c * 32 + q4 * 8;
+            if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + q4 * 8, inv);
+          }
         }
       }
-      if (qt == 0 && m < p.M)
-        p.lse[(static_cast<int64_t>(bh)) * p.M + m] = any_key ? m_used + log2f(l) : INFINITY;
+      // O is in registers / stored: the next unit's first P V product may overwrite it (it is
+      // issued after all four warps have announced that unit's first P)
+      tc_fence_before();
+      if (m < p.M) p.lse[static_cast<int64_t>(u.bh) * p.M + m] = any_key ? m_used + log2f(l) : INFINITY;
     }
-    }  // tiles
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 17) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int DP, typename T, int BIAS>
@@ -514,7 +582,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  return launch_overlapped(kern, grid, 640, L::kDynamic, stream, fp);
+  return launch_overlapped(kern, grid, 352, L::kDynamic, stream, fp);
 }
 
 template <int DP, typename T>
@@ -529,14 +597,13 @@ int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stre
 
 }  // namespace
 
-
 int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   FwdParams fp;
   int r = make_tmap_bshd(&fp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
   if (r) return r;
   r = make_tmap_bshd(&fp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, 128);
   if (r) return r;
-  r = make_tmap_bshd(&fp.map_v, p.v, p.B, p.N, p.H, p.D, p.v_stride, 128);
+  r = make_tmap_bshd(&fp.map_v, p.v, p.B, p.N, p.H, p.D, p.v_stride, 64);
   if (r) return r;
   fp.bias_b_mul = fp.bias_h_mul = 0;
   if (p.bias_kind == FA_BIAS_SAME) {
@@ -566,8 +633,9 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   fp.causal = p.causal ? 1 : 0;
   fp.sm_scale = p.sm_scale;
   fp.n_mblk = (p.M + 127) / 128;
-  fp.n_tiles = fp.n_mblk * p.B * p.H;
-  const dim3 grid(persistent_grid(p.causal ? (fp.n_tiles + 1) / 2 : fp.n_tiles));
+  fp.n_pairs = (fp.n_mblk + 1) / 2;
+  fp.n_units = fp.n_pairs * p.B * p.H;
+  const dim3 grid(persistent_grid(p.causal ? (fp.n_units + 1) / 2 : fp.n_units));
   const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {
     return dp == 64 ? launch_bias<64, __nv_bfloat16>(fp, p.bias_kind, grid, stream)
