@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[3], v_empty[3];
   __shared__ uint64_t s_full[2], p_full[2][2], pv_done[2][2];
-  __shared__ uint64_t bias_full[3], bias_empty[3];
+  __shared__ uint64_t bias_full[2][3], bias_empty[3];  // full: one set per consuming group
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -194,7 +194,8 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
     for (int i = 0; i < 3; ++i) {
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&bias_full[i], 1);
+      mbar_init(&bias_full[0][i], 1);
+      mbar_init(&bias_full[1][i], 1);
       mbar_init(&bias_empty[i], 4);
     }
     mbar_fence_init();
@@ -352,9 +353,10 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
         if (!ok) break;
         int n0, m0, hh, bb;
         cur.coords(p, n0, m0, hh, bb);
-        mbar_expect_tx(&bias_full[bs], kBlk);
-        tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, &bias_full[bs], n0, m0, hh, bb,
-                         pol_stream);
+        // the "full" barrier of the group that will read this unit (see the softmax side)
+        uint64_t* full = &bias_full[cur.t][bs];
+        mbar_expect_tx(full, kBlk);
+        tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, full, n0, m0, hh, bb, pol_stream);
         cur.next(p);
       }
     }
@@ -371,6 +373,13 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
     const float scale_log2 = p.sm_scale * kLog2e;
     uint32_t cs = 0;  // steps done by this tile slot, over all units
     uint32_t bu = 0;  // bias units before the current key block, over all units and both tiles
+    // The ring slots are shared by both groups, the "full" barriers are not: bias_full[t][slot]
+    // completes once per unit of tile slot t that lands in that ring slot, so its only waiter
+    // (this group) is never more than one completion behind and a parity wait is safe.  (With
+    // one barrier per slot a group could ask for completion k+1 before completion k - the other
+    // group's unit - had happened, which a parity wait cannot tell from "done".)  Bit s of
+    // b_phase is the parity of this group's next unit in slot s.
+    uint32_t b_phase = 0;
     Unit u;
     for (int it = 0; ok && unit_at(p, it, u); ++it) {
       const int nblk = u.nb(t);
@@ -387,9 +396,9 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
             const uint32_t unit = BIAS == 1 ? first + h : first;
-            const uint32_t bs = unit % NB, b_par = (unit / NB) & 1;
+            const uint32_t bs = unit % NB, b_par = (b_phase >> bs) & 1;
             uint32_t pbias = 1;
-            if (BIAS != 0 && (BIAS == 1 || h == 0)) pbias = mbar_poll(&bias_full[bs], b_par);
+            if (BIAS != 0 && (BIAS == 1 || h == 0)) pbias = mbar_poll(&bias_full[t][bs], b_par);
             float s[64];
             tmem_ld32(tm_s + h * 64, reinterpret_cast<uint32_t*>(s));
             tmem_ld32(tm_s + h * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
@@ -408,7 +417,7 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
               }
             } else {
               if (BIAS == 1 || h == 0) {
-                ok = wait_warp_polled(pbias, &bias_full[bs], b_par, ctx, kSiteBiasFull, j);
+                ok = wait_warp_polled(pbias, &bias_full[t][bs], b_par, ctx, kSiteBiasFull, j);
                 if (!ok) break;
               }
               const uint32_t row = smem_u32(smem + L::kBias + bs * kBlk) + static_cast<uint32_t>(r) * 128u;
@@ -445,6 +454,7 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
                 }
               }
               if (BIAS == 1 || h == 1) {
+                b_phase ^= 1u << bs;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bias_empty[bs]);
               }
