@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FA_ABI_VERSION 1
+#define FA_ABI_VERSION 2
 
 enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 };
 
@@ -30,7 +30,8 @@ enum fa_bias_kind {
   FA_BIAS_NONE = 0,
   FA_BIAS_SAME = 1, /* float bias in the same 16-bit dtype as q; added to q.k^T*scale      */
   FA_BIAS_BOOL = 2, /* one byte per element; 0 masks the score out, non-zero keeps it      */
-  FA_BIAS_F32 = 3   /* fp32 bias with 16-bit q/k/v (bias gradient, when asked for, is fp32) */
+  FA_BIAS_F32 = 3   /* fp32 bias with 16-bit q/k/v: streamed as fp32, never rounded to 16 bits;
+                       the bias gradient, when asked for, is written in fp32 (FA:52, FA:292, FA:799) */
 };
 
 enum fa_error {
@@ -52,7 +53,11 @@ enum fa_error {
  *   q, o, do, dq : (B, M, H, D)  strides {B, M, H}
  *   k, v, dk, dv : (B, N, H, D)  strides {B, N, H}
  *   bias, dbias  : (B, H, M, N)  strides {B, H, M}; a stride of 0 (an expanded
- *                  view) is accepted for B and H of `bias`
+ *                  view) is accepted for B and H of `bias`.  dbias has the bias's
+ *                  element type (16-bit for FA_BIAS_SAME, fp32 for FA_BIAS_F32).  With
+ *                  FA_BIAS_F32 and causal = 1 the caller zero-fills dbias first: tiles
+ *                  above the diagonal are not visited (with FA_BIAS_SAME the library
+ *                  writes those zeros itself)
  *   lse, delta   : (B, H, M) fp32, contiguous
  * Alignment: q/k/v/do base pointers and strides*2 bytes are multiples of 16; the
  * same holds for bias/dbias strides in bytes (the Python layer pads when a row
@@ -91,6 +96,14 @@ typedef struct fa_params {
   int64_t dv_stride[3];
   int64_t bias_stride[3];
   int64_t dbias_stride[3];
+
+  /* Backward with FA_BIAS_F32 only (required there, ignored otherwise): a (B,H,M,N) scratch
+   * tensor in q's 16-bit dtype.  The dK/dV stage leaves dS there for the dQ stage (which
+   * consumes dS as a 16-bit tensor-core operand, exactly as the reference rounds dS before
+   * its dQ product, FA:517).  Same stride rules as dbias.  Contents afterwards: dS rounded to
+   * 16 bits at and below the causal diagonal, unspecified above it. */
+  void* ds16;
+  int64_t ds16_stride[3];
 } fa_params;
 
 /* Library / ABI version (FA_ABI_VERSION of the build). */

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_version_and_status_strings():
     lib = _cabi.load()
-    assert lib.fa_version() == 1
+    assert lib.fa_version() == 2
     assert _cabi.status_string(0) == "ok"
     for code in range(1, 10):
         assert _cabi.status_string(code) not in ("ok", "unknown error code")
@@ -42,13 +42,15 @@ def test_struct_layout_matches_the_header(tmp_path):
     src = tmp_path / "sz.c"
     src.write_text(
         '#include "fa_sm100.h"\n#include <stdio.h>\n#include <stddef.h>\n'
-        "int main(void){printf(\"%zu %zu %zu %zu %zu\\n\", sizeof(fa_params), offsetof(fa_params, sm_scale),"
-        " offsetof(fa_params, q), offsetof(fa_params, delta), offsetof(fa_params, dbias_stride));return 0;}\n")
+        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(fa_params), offsetof(fa_params, sm_scale),"
+        " offsetof(fa_params, q), offsetof(fa_params, delta), offsetof(fa_params, dbias_stride),"
+        " offsetof(fa_params, ds16), offsetof(fa_params, ds16_stride));return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
     c = [int(x) for x in subprocess.check_output([str(exe)]).split()]
     P = _cabi.FaParams
-    assert c == [ctypes.sizeof(P), P.sm_scale.offset, P.q.offset, P.delta.offset, P.dbias_stride.offset]
+    assert c == [ctypes.sizeof(P), P.sm_scale.offset, P.q.offset, P.delta.offset, P.dbias_stride.offset,
+                 P.ds16.offset, P.ds16_stride.offset]
 
 
 def _params(**kw):

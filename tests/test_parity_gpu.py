@@ -125,15 +125,43 @@ def test_expanded_bias_and_fp32_bias(device_ok):
     assert (out.float() - ref["out"]).abs().max().item() <= 5e-3
     assert b0.grad.shape == b0.shape
     assert (b0.grad.float() - ref["dbias"].sum((0, 1), keepdim=True)).abs().max().item() <= 2e-2
-    # fp32 bias with fp16 q: gradient comes back in fp32
-    b32 = torch.randn(B, H, M, N, generator=torch.Generator().manual_seed(99)).cuda().requires_grad_()
-    out = flash_attention_fn(q, k, v, b32, False, 0.3)
+
+
+@pytest.mark.parametrize("dtype,D,M,N,causal", [(HF, 64, 128, 256, False), (BF, 128, 300, 200, True),
+                                               (BF, 64, 200, 330, False), (HF, 32, 129, 70, True)])
+def test_fp32_bias_is_streamed_in_fp32_and_its_gradient_is_fp32(dtype, D, M, N, causal, device_ok):
+    """A float bias in another dtype than q (the reference adds it in fp32, flash_attention.py
+    lines 52 and 292, and returns its gradient in the bias's dtype, line 799) is never rounded to
+    16 bits: fp32 in, fp32 dS out.  The gradient therefore meets the absolute bound without the
+    16-bit rounding allowance, and a bias with digits a 16-bit type cannot hold changes the output."""
+    from triton_flashattn_b200 import flash_attention_fn
+
+    B, H = 2, 2
+    q, k, v, _, do = make_inputs(B, M, N, H, D, dtype, None, 9)
+    g = torch.Generator().manual_seed(99)
+    b32 = torch.randn(B, H, M, N, generator=g).cuda()
+    qq, kk, vv, bb = (t.clone().requires_grad_() for t in (q, k, v, b32))
+    out = flash_attention_fn(qq, kk, vv, bb, causal, 0.3)
     out.backward(do)
-    ref = oracle.attention_backward(q, k, v, b32.detach(), False, 0.3, do)
-    assert b32.grad.dtype == torch.float32
-    assert (out.float() - ref["out"]).abs().max().item() <= 5e-3
-    # the fp32 bias is streamed in q's 16-bit dtype, so it is rounded once on the way in
-    assert (b32.grad - ref["dbias"]).abs().max().item() <= 1e-2
+    ref = oracle.attention_backward(q, k, v, b32, causal, 0.3, do)
+    assert bb.grad.dtype == torch.float32 and bb.grad.is_contiguous() and bb.grad.shape == b32.shape
+    ours = {"out": out.detach(), "dq": qq.grad, "dk": kk.grad, "dv": vv.grad}
+    for n, t in ours.items():
+        accept(n, account(t, ref[n], dtype), dtype, label=f"fp32 bias {dtype} {n}: ")
+    err = (bb.grad - ref["dbias"]).abs().max().item()
+    print(f"fp32 dbias max-abs error {err:.2e}")
+    assert err <= TOL[dtype] / 2, err  # no 16-bit rounding of dS: well inside the bound
+    if causal:
+        assert torch.all(bb.grad[0, 0].triu(1) == 0)
+    # the low bits of the fp32 bias matter: rounding it to 16 bits first gives another result
+    out16 = flash_attention_fn(q, k, v, b32.to(dtype), causal, 0.3)
+    assert not torch.equal(out16, out.detach())
+    # a float64 bias takes the same path and gets a float64 gradient
+    b64 = b32.double().requires_grad_()
+    out64 = flash_attention_fn(q, k, v, b64, causal, 0.3)
+    out64.backward(do)
+    assert b64.grad.dtype == torch.float64 and torch.equal(out64, out.detach())
+    assert torch.equal(b64.grad.float(), bb.grad)
 
 
 def test_fully_masked_row_is_zero_not_nan(device_ok):

@@ -57,6 +57,8 @@ class FaParams(ctypes.Structure):
         ("dv_stride", _I64x3),
         ("bias_stride", _I64x3),
         ("dbias_stride", _I64x3),
+        ("ds16", ctypes.c_void_p),
+        ("ds16_stride", _I64x3),
     ]
 
 

@@ -115,7 +115,6 @@ int validate_common(const fa_params* p) {
   if (p->D == 256) return FA_ERR_UNSUPPORTED;
   if (p->dtype != FA_F16 && p->dtype != FA_BF16) return FA_ERR_DTYPE;
   if (p->bias_kind < FA_BIAS_NONE || p->bias_kind > FA_BIAS_F32) return FA_ERR_DTYPE;
-  if (p->bias_kind == FA_BIAS_F32) return FA_ERR_UNSUPPORTED;
   if (!p->q || !p->k || !p->v || !p->o || !p->lse) return FA_ERR_NULL;
   if (p->bias_kind != FA_BIAS_NONE && !p->bias) return FA_ERR_NULL;
   if ((int64_t)p->B * p->H > 65535) return FA_ERR_TOO_LARGE;
@@ -127,9 +126,10 @@ int validate_bwd(const fa_params* p) {
   if (r) return r;
   if (!p->d_o || !p->dq || !p->dk || !p->dv || !p->delta) return FA_ERR_NULL;
   if (p->write_dbias) {
-    if (p->bias_kind != FA_BIAS_SAME) return FA_ERR_DTYPE;
+    if (p->bias_kind != FA_BIAS_SAME && p->bias_kind != FA_BIAS_F32) return FA_ERR_DTYPE;
     if (!p->dbias) return FA_ERR_NULL;
   }
+  if (p->bias_kind == FA_BIAS_F32 && !p->ds16) return FA_ERR_NULL;
   return FA_OK;
 }
 
@@ -163,7 +163,7 @@ const char* fa_status_string(int code) {
     case FA_ERR_ALIGN: return "pointer or stride is not a multiple of 16 bytes";
     case FA_ERR_CUDA: return "a CUDA call failed";
     case FA_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait";
-    case FA_ERR_UNSUPPORTED: return "not supported by this build (head dim 256 / fp32 bias)";
+    case FA_ERR_UNSUPPORTED: return "not supported by this build (head dim 256)";
     case FA_ERR_TOO_LARGE: return "size exceeds a limit of this entry point";
     default: return "unknown error code";
   }

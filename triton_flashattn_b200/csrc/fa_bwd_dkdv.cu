@@ -59,7 +59,11 @@ struct DkdvParams {
   int64_t dk_sB, dk_sN, dk_sH, dv_sB, dv_sN, dv_sH;
   int H, M, N, D;
   int n_nblk, n_tiles;  // key blocks per (batch, head); tiles = n_nblk * B * H
-  int causal, write_dbias, bias_vec32, bias_b_mul, bias_h_mul;
+  int causal, bias_vec32, bias_b_mul, bias_h_mul;
+  int store_ds;    // the 16-bit dS tiles go out through map_dbias (as dbias, or as scratch for dQ)
+  int zero_tiles;  // ... and zero tiles go to the causally skipped part (16-bit dbias only)
+  float* dbias_f32;  // fp32 bias gradient, written from registers (fp32 bias only), or null
+  int64_t dbf_sB, dbf_sH, dbf_sM;
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
 };
@@ -92,7 +96,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   constexpr uint32_t kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
   constexpr uint32_t kTmemCols = 512;
   // BIAS: 0 none; 1 16-bit bias, brought in by TMA (warp 19; the dbias stores then move to
-  // warp 18); 2 byte mask, read by the row threads from global memory
+  // warp 18); 2 byte mask and 3 fp32 bias, read by the row threads from global memory (the mask
+  // one step ahead, the fp32 row - 32 registers - at the start of its own step)
   constexpr int BK = BIAS;
 
   extern __shared__ uint8_t smem_raw[];
@@ -193,9 +198,11 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         // tiles of the next one (pf_done of them are out when that tile starts).
         auto bias_l2 = [&](int b_, int h_, int n0_, int mblk) {
           const int mp = mblk * 128;
-          tma_prefetch_l2_4d(&p.map_bias, n0_, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
-          if (BK == 1 && n0_ + 64 < p.N)
-            tma_prefetch_l2_4d(&p.map_bias, n0_ + 64, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
+          constexpr int kBox = BK == 1 ? 64 : (BK == 3 ? 32 : 128);  // keys per box of map_bias
+#pragma unroll
+          for (int c = 0; c < 128; c += kBox)
+            if (c == 0 || n0_ + c < p.N)
+              tma_prefetch_l2_4d(&p.map_bias, n0_ + c, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
         };
         if (BIAS != 0) {
           for (int t = pf_done; t < kBiasAhead && t < T_steps; ++t) bias_l2(b, h, n0, i_start + t);
@@ -301,14 +308,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       // completions in a row that no row thread has to wait for in between would let a parity
       // wait fall two phases behind.)  The wait for the store's read sits right after the
       // store: the next thing this thread needs, P of the next step, is further away.
-      const bool stores_here = BIAS == 1 && p.write_dbias;
+      const bool stores_here = p.store_ds != 0;
       bool zeros_in_flight = false;
       bool ok = true;
       uint32_t g = 0;
       int bh, nb, i_start, T_steps;
       for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
         const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
-        if (stores_here && p.causal) {
+        if (p.zero_tiles) {
           ok = mbar_wait(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
           if (!ok) break;
           for (int i = 0; i < i_start; ++i) {
@@ -423,7 +430,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const int64_t bias_bh = b_ * p.bias_sB + h_ * p.bias_sH;
       const int m = mblk * 128 + r;
       const bool row_ok = m < p.M;
-      if constexpr (BR != 0) {
+      if constexpr (BR == 2) {
         load_bias_row<BK>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, c0, p.N,
                           p.bias_vec32 != 0);
       }
@@ -440,7 +447,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
 #pragma unroll 1
     for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
       const int col0 = nb * 128 + qt * 32;
-      if (p.write_dbias && p.causal) {
+      if (p.zero_tiles) {
         // sDS becomes the zero tile for the causally skipped part of dbias: the last dbias
         // store of the previous tile must have read it (the last dK product has: its barrier
         // was seen in that tile's epilogue).  Causal completions of st_done: tile `it` owns
@@ -460,6 +467,12 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         const int t = mb - i0;
         const int m0 = mb * 128;
         BiasRegs<BR> bcur = bnext;
+        if constexpr (BR == 3) {
+          // fp32 bias row of this step: asked for now, used once S has arrived
+          const int b_ = bh / p.H, h_ = bh - b_ * p.H;
+          load_bias_row<3>(bcur, p.bias, b_ * p.bias_sB + h_ * p.bias_sH + (int64_t)(m0 + r) * p.bias_sM,
+                           m0 + r < p.M, col0, p.N, p.bias_vec32 != 0);
+        }
         const float neg_lse = lse_next, delta_r = delta_next;
         if (mb + 1 < n_mblk) prefetch(bh, col0, mb + 1);
         // S and "dV of the previous step has read P" are usually true by now: one combined look
@@ -514,7 +527,9 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         } else {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+          f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
+          if (BK == 3)
+            a = ffma2(f2(__uint_as_float(bcur.w[i]), __uint_as_float(bcur.w[i + 1])), f2(kLog2e, kLog2e), a);
           // every fourth pair on the FMA pipe, the rest on the special-function unit
           const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
           if (BK == 2) {
@@ -552,8 +567,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         uint32_t pdp = 0, pdk = 1, pst = 1;
         // sDS may be rewritten once its previous dbias store has read it: causal -> completion
         // gs+it of st_done (see above); otherwise completion gs-1 (the store of step gs-1)
-        const uint32_t st_par = (p.causal ? gs + it : gs - 1) & 1;
-        const bool st_wait = p.write_dbias && (p.causal || gs >= 1);
+        const uint32_t st_par = (p.zero_tiles ? gs + it : gs - 1) & 1;
+        const bool st_wait = p.store_ds && (p.zero_tiles || gs >= 1);
         if (t >= 1 && st_wait)
           mbar_poll3(&dp_full, gs & 1, &dk_done, (gs - 1) & 1, &st_done, st_par, pdp, pdk, pst);
         else if (t >= 1)
@@ -584,6 +599,25 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
                                   fadd2(f2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1])),
                                         f2(-delta_r, -delta_r)));
             dsu[hf * 8 + i] = P2::pack(f2_lo(d), f2_hi(d));
+            if (BIAS == 3) {
+              dp[2 * i] = __float_as_uint(f2_lo(d));
+              dp[2 * i + 1] = __float_as_uint(f2_hi(d));
+            }
+          }
+          if (BIAS == 3 && p.dbias_f32 != nullptr && m0 + r < p.M) {
+            // the fp32 bias gradient goes out unrounded, 64 contiguous bytes per thread and half
+            const int b_ = bh / p.H, h_ = bh - b_ * p.H;
+            const int c0 = col0 + hf * 16;
+            float* drow = p.dbias_f32 + b_ * p.dbf_sB + h_ * p.dbf_sH + (int64_t)(m0 + r) * p.dbf_sM + c0;
+            if (c0 + 16 <= p.N) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                *reinterpret_cast<uint4*>(drow + 4 * k) = make_uint4(dp[4 * k], dp[4 * k + 1], dp[4 * k + 2], dp[4 * k + 3]);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k)
+                if (c0 + k < p.N) drow[k] = __uint_as_float(dp[k]);
+            }
           }
         }
         if (t >= 1) {
@@ -679,6 +713,7 @@ int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t str
     case FA_BIAS_NONE: return launch_inst<DP, T, 0>(kp, grid, stream);
     case FA_BIAS_SAME: return launch_inst<DP, T, 1>(kp, grid, stream);
     case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(kp, grid, stream);
+    case FA_BIAS_F32: return launch_inst<DP, T, 3>(kp, grid, stream);
     default: return FA_ERR_UNSUPPORTED;
   }
 }
@@ -696,14 +731,31 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   if (r) return r;
   r = make_tmap_bshd(&kp.map_do, p.d_o, p.B, p.M, p.H, p.D, p.do_stride, 128);
   if (r) return r;
-  if (p.write_dbias) {
+  const bool f32 = p.bias_kind == FA_BIAS_F32;
+  kp.store_ds = f32 ? 1 : (p.write_dbias ? 1 : 0);
+  kp.zero_tiles = !f32 && p.write_dbias && p.causal;
+  kp.dbias_f32 = nullptr;
+  kp.dbf_sB = kp.dbf_sH = kp.dbf_sM = 0;
+  if (kp.store_ds) {
+    // the 16-bit dS tiles: the bias gradient itself, or (fp32 bias) the scratch the dQ stage reads
+    const void* dst = f32 ? p.ds16 : p.dbias;
+    const int64_t* dst_stride = f32 ? p.ds16_stride : p.dbias_stride;
+    if (!dst) return FA_ERR_NULL;
     int bm, hm;
-    r = make_tmap_bhmn(&kp.map_dbias, p.dbias, 2, p.B, p.H, p.M, p.N, p.dbias_stride, 64, 128, &bm,
-                       &hm);
+    r = make_tmap_bhmn(&kp.map_dbias, dst, 2, p.B, p.H, p.M, p.N, dst_stride, 64, 128, &bm, &hm);
     if (r) return r;
-    if (!bm || !hm) return FA_ERR_ALIGN;  // dbias must be a real (B,H,M,N) tensor
+    if (!bm || !hm) return FA_ERR_ALIGN;  // must be a real (B,H,M,N) tensor
   } else {
     kp.map_dbias = kp.map_q;
+  }
+  if (f32 && p.write_dbias) {
+    if (reinterpret_cast<uintptr_t>(p.dbias) % 16 != 0 || p.dbias_stride[0] % 4 || p.dbias_stride[1] % 4 ||
+        p.dbias_stride[2] % 4)
+      return FA_ERR_ALIGN;
+    kp.dbias_f32 = static_cast<float*>(p.dbias);
+    kp.dbf_sB = p.dbias_stride[0];
+    kp.dbf_sH = p.dbias_stride[1];
+    kp.dbf_sM = p.dbias_stride[2];
   }
   auto bad = [](const void* ptr, const int64_t s[3]) {
     return reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || s[0] % 8 || s[1] % 8 || s[2] % 8;
@@ -719,9 +771,13 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
     r = make_tmap_bhmn(&kp.map_bias, p.bias, 1, p.B, p.H, p.M, p.N, p.bias_stride, 128, 128,
                        &kp.bias_b_mul, &kp.bias_h_mul);
     if (r) return r;
+  } else if (f32) {
+    r = make_tmap_bhmn(&kp.map_bias, p.bias, 4, p.B, p.H, p.M, p.N, p.bias_stride, 32, 128,
+                       &kp.bias_b_mul, &kp.bias_h_mul);
+    if (r) return r;
   }
   if (p.bias_kind != FA_BIAS_NONE) {
-    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
+    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : (f32 ? 4 : 2);
     if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || (p.bias_stride[0] * eb) % 16 ||
         (p.bias_stride[1] * eb) % 16 || (p.bias_stride[2] * eb) % 16)
       return FA_ERR_ALIGN;
@@ -746,9 +802,8 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
   kp.N = p.N;
   kp.D = p.D;
   kp.causal = p.causal ? 1 : 0;
-  kp.write_dbias = p.write_dbias ? 1 : 0;
   {
-    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
+    const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : (f32 ? 4 : 2);
     kp.bias_vec32 = p.bias_kind != FA_BIAS_NONE && reinterpret_cast<uintptr_t>(p.bias) % 32 == 0 &&
                     (p.bias_stride[0] * eb) % 32 == 0 && (p.bias_stride[1] * eb) % 32 == 0 &&
                     (p.bias_stride[2] * eb) % 32 == 0;

@@ -560,9 +560,12 @@ int launch_bias(const DqParams& kp, int bias_kind, bool from_ds, dim3 grid, cuda
 
 int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   DqParams kp;
-  // When dS has just been written as dbias (same 16-bit dtype as q) the streamed GEMM
-  // variant is used, otherwise the general kernel.
-  const bool from_ds = p.write_dbias && p.bias_kind == FA_BIAS_SAME;
+  // When the dK/dV stage has just left dS in a 16-bit tensor (the bias gradient itself, or the
+  // scratch an fp32 bias comes with) the streamed GEMM variant is used, otherwise the general
+  // kernel.
+  const bool f32 = p.bias_kind == FA_BIAS_F32;
+  if (f32 && !p.ds16) return FA_ERR_NULL;
+  const bool from_ds = f32 || (p.write_dbias && p.bias_kind == FA_BIAS_SAME);
   int r = make_tmap_bshd(&kp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
   if (r) return r;
   r = make_tmap_bshd(&kp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, from_ds ? 64 : 128);
@@ -573,8 +576,8 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   if (r) return r;
   if (from_ds) {
     int bm, hm;
-    r = make_tmap_bhmn(&kp.map_ds, p.dbias, 2, p.B, p.H, p.M, p.N, p.dbias_stride, 64, 128, &bm,
-                       &hm);
+    r = make_tmap_bhmn(&kp.map_ds, f32 ? p.ds16 : p.dbias, 2, p.B, p.H, p.M, p.N,
+                       f32 ? p.ds16_stride : p.dbias_stride, 64, 128, &bm, &hm);
     if (r) return r;
     if (!bm || !hm) return FA_ERR_ALIGN;
   } else {
@@ -583,7 +586,7 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   if (reinterpret_cast<uintptr_t>(p.dq) % 16 != 0 || p.dq_stride[0] % 8 || p.dq_stride[1] % 8 ||
       p.dq_stride[2] % 8)
     return FA_ERR_ALIGN;
-  if (p.bias_kind != FA_BIAS_NONE) {
+  if (p.bias_kind != FA_BIAS_NONE && !f32) {
     const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
     if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || (p.bias_stride[0] * eb) % 16 ||
         (p.bias_stride[1] * eb) % 16 || (p.bias_stride[2] * eb) % 16)

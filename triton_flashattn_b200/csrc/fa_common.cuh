@@ -667,10 +667,11 @@ __device__ __forceinline__ bool wait_warp_polled(uint32_t polled, uint64_t* bar,
   return wait_warp(bar, parity, ctx, site, iter);
 }
 
-// 32 bias values of one row quarter, as raw 16-bit pairs (BIAS == 1) or bytes (BIAS == 2).
+// 32 bias values of one row quarter, as raw 16-bit pairs (BIAS == 1), bytes (BIAS == 2) or
+// fp32 words (BIAS == 3).
 template <int BIAS>
 struct BiasRegs {
-  uint32_t w[BIAS == 1 ? 16 : (BIAS == 2 ? 8 : 1)];
+  uint32_t w[BIAS == 1 ? 16 : (BIAS == 2 ? 8 : (BIAS == 3 ? 32 : 1))];
 };
 
 // Reads bias[row][col0 .. col0+31] straight from global memory; out-of-range elements
@@ -680,9 +681,9 @@ template <int BIAS>
 __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bias_base,
                                               int64_t row_off, bool row_ok, int col0, int N,
                                               bool vec32) {
-  constexpr int kElem = BIAS == 1 ? 2 : 1;     // bytes per element
-  constexpr int kWords = BIAS == 1 ? 16 : 8;   // 32-bit words per 32 elements
-  constexpr int kPerWord = 4 / kElem;          // elements per word
+  constexpr int kElem = BIAS == 1 ? 2 : (BIAS == 3 ? 4 : 1);  // bytes per element
+  constexpr int kWords = 8 * kElem;                           // 32-bit words per 32 elements
+  constexpr int kPerWord = 4 / kElem;                         // elements per word
   if (BIAS == 0) return;
   const uint8_t* rowp = reinterpret_cast<const uint8_t*>(bias_base) + row_off * kElem;
   if (!row_ok || col0 >= N) {
@@ -714,9 +715,10 @@ __device__ __forceinline__ void load_bias_row(BiasRegs<BIAS>& br, const void* bi
     for (int k = 0; k < kPerWord; ++k) {
       const int col = col0 + i * kPerWord + k;
       if (col < N) {
-        const uint32_t e = BIAS == 1 ? (uint32_t)__ldcg(reinterpret_cast<const uint16_t*>(rowp) + col)
-                                     : (uint32_t)__ldcg(rowp + col);
-        word |= e << (8 * kElem * k);
+        const uint32_t e = BIAS == 1   ? (uint32_t)__ldcg(reinterpret_cast<const uint16_t*>(rowp) + col)
+                           : BIAS == 3 ? __ldcg(reinterpret_cast<const uint32_t*>(rowp) + col)
+                                       : (uint32_t)__ldcg(rowp + col);
+        word |= e << ((8 * kElem * k) & 31);
       }
     }
     br.w[i] = word;

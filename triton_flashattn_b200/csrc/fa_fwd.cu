@@ -99,10 +99,11 @@ __device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
 }
 
 // Walks the bias units of this CTA in the order the softmax groups consume them:
-// per unit, per key block j, per tile t (if it visits j), per 64-key half (16-bit bias)
-// or once (byte mask, one [128][128] unit per block).
+// per unit, per key block j, per tile t (if it visits j): two 64-key halves (16-bit bias),
+// four 32-key quarters (fp32 bias) or one unit (byte mask, [128][128] bytes per block).
 template <int BIAS>
 struct BiasWalk {
+  static constexpr int kSub = BIAS == 1 ? 2 : (BIAS == 3 ? 4 : 1);  // units per (tile, block)
   int it = 0, j = 0, t = 0, h = 0;
   Unit u;
   bool valid = false;
@@ -133,8 +134,8 @@ struct BiasWalk {
     settle(p);
   }
   __device__ __forceinline__ void next(const FwdParams& p) {
-    if (BIAS == 1 && h == 0) {
-      h = 1;
+    if (h + 1 < kSub) {
+      ++h;
       return;
     }
     h = 0;
@@ -144,7 +145,7 @@ struct BiasWalk {
   // coordinates of the current unit's box: (key, row, head, batch)
   __device__ __forceinline__ void coords(const FwdParams& p, int& n0, int& m0, int& hh, int& bb) const {
     const int b = u.bh / p.H;
-    n0 = j * 128 + h * 64;
+    n0 = j * 128 + h * (128 / kSub);
     m0 = (u.mb0 + t) * 128;
     hh = (u.bh - b * p.H) * p.bias_h_mul;
     bb = b * p.bias_b_mul;
@@ -367,7 +368,8 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     const uint32_t tm_s = tmem_addr(tmem, lane_base, t * 128);
     const uint32_t tm_o = tmem_addr(tmem, lane_base, 256 + t * 128);
-    constexpr int kU = BIAS == 1 ? 2 : 1;    // bias units per (tile, key block)
+    constexpr int kU = BIAS == 1 ? 2 : (BIAS == 3 ? 4 : 1);  // bias units per (tile, key block)
+    constexpr int kUH = kU / 2;  // units per 64-key half (0: one unit serves both halves)
     bool ok = live;
     const bool fold_scale = p.sm_scale > 0.f;  // no-bias path: maximum taken on raw q.k
     const float scale_log2 = p.sm_scale * kLog2e;
@@ -395,10 +397,10 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
           tc_fence_after();
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
-            const uint32_t unit = BIAS == 1 ? first + h : first;
-            const uint32_t bs = unit % NB, b_par = (b_phase >> bs) & 1;
+            const uint32_t unit = first + h * kUH;
+            uint32_t bs = unit % NB, b_par = (b_phase >> bs) & 1;
             uint32_t pbias = 1;
-            if (BIAS != 0 && (BIAS == 1 || h == 0)) pbias = mbar_poll(&bias_full[t][bs], b_par);
+            if (BIAS != 0 && (BIAS != 2 || h == 0)) pbias = mbar_poll(&bias_full[t][bs], b_par);
             float s[64];
             tmem_ld32(tm_s + h * 64, reinterpret_cast<uint32_t*>(s));
             tmem_ld32(tm_s + h * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
@@ -416,12 +418,40 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
                 for (int i = 0; i < 64; ++i) s[i] *= p.sm_scale;
               }
             } else {
-              if (BIAS == 1 || h == 0) {
+              if (BIAS != 2 || h == 0) {
                 ok = wait_warp_polled(pbias, &bias_full[t][bs], b_par, ctx, kSiteBiasFull, j);
                 if (!ok) break;
               }
               const uint32_t row = smem_u32(smem + L::kBias + bs * kBlk) + static_cast<uint32_t>(r) * 128u;
-              if (BIAS == 1) {
+              if (BIAS == 3) {
+                // fp32 bias: two [128 rows][32 keys] units per half, four floats per 16-byte chunk
+                const f32x2 sc2 = f2(p.sm_scale, p.sm_scale);
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                  if (sub == 1) {
+                    bs = (unit + 1) % NB;
+                    b_par = (b_phase >> bs) & 1;
+                    ok = wait_warp(&bias_full[t][bs], b_par, ctx, kSiteBiasFull, j);
+                    if (!ok) break;
+                  }
+                  const uint32_t row3 = smem_u32(smem + L::kBias + bs * kBlk) + static_cast<uint32_t>(r) * 128u;
+#pragma unroll
+                  for (int c = 0; c < 8; ++c) {
+                    const uint4 v = lds128(row3 + (static_cast<uint32_t>(c ^ (r & 7)) << 4));
+                    const int i = sub * 32 + c * 4;
+                    const f32x2 x0 = ffma2(f2(s[i], s[i + 1]), sc2, f2(__uint_as_float(v.x), __uint_as_float(v.y)));
+                    const f32x2 x1 = ffma2(f2(s[i + 2], s[i + 3]), sc2, f2(__uint_as_float(v.z), __uint_as_float(v.w)));
+                    s[i] = f2_lo(x0);
+                    s[i + 1] = f2_hi(x0);
+                    s[i + 2] = f2_lo(x1);
+                    s[i + 3] = f2_hi(x1);
+                  }
+                  b_phase ^= 1u << bs;
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&bias_empty[bs]);
+                }
+                if (!ok) break;
+              } else if (BIAS == 1) {
                 const f32x2 sc2 = f2(p.sm_scale, p.sm_scale);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -453,7 +483,7 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
                   }
                 }
               }
-              if (BIAS == 1 || h == 1) {
+              if (BIAS == 1 || (BIAS == 2 && h == 1)) {
                 b_phase ^= 1u << bs;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bias_empty[bs]);
@@ -601,6 +631,7 @@ int launch_bias(const FwdParams& fp, int bias_kind, dim3 grid, cudaStream_t stre
     case FA_BIAS_NONE: return launch_inst<DP, T, 0>(fp, grid, stream);
     case FA_BIAS_SAME: return launch_inst<DP, T, 1>(fp, grid, stream);
     case FA_BIAS_BOOL: return launch_inst<DP, T, 2>(fp, grid, stream);
+    case FA_BIAS_F32: return launch_inst<DP, T, 3>(fp, grid, stream);
     default: return FA_ERR_UNSUPPORTED;
   }
 }
@@ -622,6 +653,10 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
     if (r) return r;
   } else if (p.bias_kind == FA_BIAS_BOOL) {
     r = make_tmap_bhmn(&fp.map_bias, p.bias, 1, p.B, p.H, p.M, p.N, p.bias_stride, 128, 128,
+                       &fp.bias_b_mul, &fp.bias_h_mul);
+    if (r) return r;
+  } else if (p.bias_kind == FA_BIAS_F32) {
+    r = make_tmap_bhmn(&fp.map_bias, p.bias, 4, p.B, p.H, p.M, p.N, p.bias_stride, 32, 128,
                        &fp.bias_b_mul, &fp.bias_h_mul);
     if (r) return r;
   } else {

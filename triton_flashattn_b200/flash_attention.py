@@ -74,9 +74,11 @@ def _classify_bias(bias, q):
     if not bias.dtype.is_floating_point:
         raise TypeError(f"bias must be a bool or floating tensor, got {bias.dtype}")
     if bias.dtype != q.dtype:
-        # The kernels stream the bias in q's 16-bit dtype; other float dtypes are
-        # converted once here (the gradient is converted back in backward).
-        bias = bias.to(q.dtype)
+        # Any other float dtype is streamed as fp32 (the reference also adds the bias in fp32,
+        # FA:52, FA:292): nothing is rounded to 16 bits, the gradient comes back in fp32.
+        if bias.dtype != torch.float32:
+            bias = bias.float()
+        return _bias_ready(bias, 4), _cabi.FA_BIAS_F32
     return _bias_ready(bias, 2), _cabi.FA_BIAS_SAME
 
 
@@ -158,8 +160,9 @@ def _flash_attn_fwd(q, k, v, bias, causal, sm_scale):
 
 def _flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbias):
     """Host launcher of the backward kernels; fills dq, dk, dv (and dbias) in place.
-    Mirrors FA:688-763.  dbias, when given, must be a (B, H, M, N) tensor in q's dtype
-    whose row pitch is a multiple of 16 bytes (see `_empty_dbias`)."""
+    Mirrors FA:688-763.  dbias, when given, must be a (B, H, M, N) tensor whose row pitch is a
+    multiple of 16 bytes (see `_empty_dbias`): in q's dtype for a bias in q's dtype, fp32 (and
+    zero-filled when causal) for any other float bias."""
     B, M, N, H, D = _check_inputs(q, k, v, bias)
     _cabi.raise_if_unhealthy(_device_index(q))
     q, k, v, o, do = (_tile_ready(t) for t in (q, k, v, o, do))
@@ -174,19 +177,32 @@ def _flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbi
     if dbias is not None:
         p.write_dbias = 1
         p.dbias, p.dbias_stride = dbias.data_ptr(), _stride3(dbias)
+    if kind == _cabi.FA_BIAS_F32:
+        # the dK/dV stage hands dS to the dQ stage through a 16-bit scratch tensor
+        ds16 = _empty_dbias(bias, q.dtype)
+        p.ds16, p.ds16_stride = ds16.data_ptr(), _stride3(ds16)
     _cabi.check(_cabi.load().fa_bwd(ctypes.byref(p), _stream(q)), "fa_bwd")
 
 
-def _empty_dbias(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    """Uninitialised (B, H, M, N) gradient buffer with a 16-byte aligned row pitch: dense
-    when N allows it, else a view of a padded buffer (the caller compacts it afterwards).
-    No zero fill is needed: the dK/dV kernel writes every tile, including the
-    causally skipped ones (the reference relies on zeros_like, FA:799)."""
+def _empty_dbias(bias: torch.Tensor, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+    """(B, H, M, N) gradient buffer with a 16-byte aligned row pitch: dense when N allows it,
+    else a view of a padded buffer (the caller compacts it afterwards).  For a 16-bit bias no
+    zero fill is needed: the dK/dV kernel writes every tile, including the causally skipped
+    ones (the reference relies on zeros_like, FA:799).  `zero`: fp32 gradient of a causal
+    problem, whose skipped tiles nobody writes."""
     B, H, M, N = bias.shape
     per16 = 16 // dtype.itemsize
     n_pad = (N + per16 - 1) // per16 * per16
-    buf = torch.empty((B, H, M, n_pad), dtype=dtype, device=bias.device)
+    make = torch.zeros if zero else torch.empty
+    buf = make((B, H, M, n_pad), dtype=dtype, device=bias.device)
     return buf[..., :N]
+
+
+def _new_dbias(bias: torch.Tensor, q: torch.Tensor, causal: bool) -> torch.Tensor:
+    """Gradient buffer for `bias` as the kernels write it: q's dtype when the bias has it, else fp32."""
+    if bias.dtype == q.dtype:
+        return _empty_dbias(bias, q.dtype)
+    return _empty_dbias(bias, torch.float32, zero=bool(causal))
 
 
 def _finish_dbias(dbias, bias):
@@ -230,7 +246,7 @@ class FlashAttentionFn(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse, bias = ctx.saved_tensors
         dq, dk, dv = _grad_like(q), _grad_like(k), _grad_like(v)
-        dbias = _empty_dbias(bias, q.dtype) if ctx.is_bias_trainable else None
+        dbias = _new_dbias(bias, q, ctx.causal) if ctx.is_bias_trainable else None
         _flash_attn_bwd(do, q, k, v, o, bias, ctx.causal, ctx.sm_scale, lse, dq, dk, dv, dbias)
         return dq, dk, dv, _finish_dbias(dbias, bias), None, None
 
@@ -263,7 +279,7 @@ class FlashAttentionQKVPackedFn(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         if not dqkv.is_contiguous():
             dqkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=qkv.device)
-        dbias = _empty_dbias(bias, qkv.dtype) if ctx.is_bias_trainable else None
+        dbias = _new_dbias(bias, qkv, ctx.causal) if ctx.is_bias_trainable else None
         _flash_attn_bwd(
             do, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, bias, ctx.causal, ctx.sm_scale, lse,
             dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2], dbias,

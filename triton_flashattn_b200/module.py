@@ -42,7 +42,7 @@ def attn_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
              need_dbias: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dq, dk, dv, dbias); dbias is an empty (0,) tensor unless `need_dbias`."""
     dq, dk, dv = _fa._grad_like(q), _fa._grad_like(k), _fa._grad_like(v)
-    dbias = _fa._empty_dbias(bias, q.dtype) if need_dbias else None
+    dbias = _fa._new_dbias(bias, q, causal) if need_dbias else None
     _fa._flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbias)
     dbias = q.new_empty((0,)) if dbias is None else _fa._finish_dbias(dbias, bias)
     return dq, dk, dv, dbias
