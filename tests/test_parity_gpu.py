@@ -137,28 +137,34 @@ def test_fp32_bias_is_streamed_in_fp32_and_its_gradient_is_fp32(dtype, D, M, N, 
     from triton_flashattn_b200 import flash_attention_fn
 
     B, H = 2, 2
+    scale = 0.3 if D <= 32 else None  # (0.3 at D >= 64 makes scores of +-10: a test of bf16, not of this path)
     q, k, v, _, do = make_inputs(B, M, N, H, D, dtype, None, 9)
     g = torch.Generator().manual_seed(99)
     b32 = torch.randn(B, H, M, N, generator=g).cuda()
     qq, kk, vv, bb = (t.clone().requires_grad_() for t in (q, k, v, b32))
-    out = flash_attention_fn(qq, kk, vv, bb, causal, 0.3)
+    out = flash_attention_fn(qq, kk, vv, bb, causal, scale)
     out.backward(do)
-    ref = oracle.attention_backward(q, k, v, b32, causal, 0.3, do)
+    ref = oracle.attention_backward(q, k, v, b32, causal, scale, do)
     assert bb.grad.dtype == torch.float32 and bb.grad.is_contiguous() and bb.grad.shape == b32.shape
     ours = {"out": out.detach(), "dq": qq.grad, "dk": kk.grad, "dv": vv.grad}
     for n, t in ours.items():
         accept(n, account(t, ref[n], dtype), dtype, label=f"fp32 bias {dtype} {n}: ")
-    err = (bb.grad - ref["dbias"]).abs().max().item()
-    print(f"fp32 dbias max-abs error {err:.2e}")
-    assert err <= TOL[dtype] / 2, err  # no 16-bit rounding of dS: well inside the bound
+    accept("dbias", account(bb.grad, ref["dbias"], dtype), dtype, label=f"fp32 bias {dtype} dbias: ")
+    # Against the oracle fed this library's own saved 16-bit output (so that the one-unit
+    # differences between two roundings of `o`, which move delta, drop out) the fp32 gradient
+    # shows no trace of a 16-bit rounding of dS: a quarter of the absolute bound, no allowance.
+    ref_saved = oracle.attention_backward(q, k, v, b32, causal, scale, do, o_saved=out.detach())
+    err = (bb.grad - ref_saved["dbias"]).abs().max().item()
+    print(f"fp32 dbias max-abs error vs oracle on the saved output {err:.2e}")
+    assert err <= TOL[dtype] / 4, err
     if causal:
         assert torch.all(bb.grad[0, 0].triu(1) == 0)
     # the low bits of the fp32 bias matter: rounding it to 16 bits first gives another result
-    out16 = flash_attention_fn(q, k, v, b32.to(dtype), causal, 0.3)
+    out16 = flash_attention_fn(q, k, v, b32.to(dtype), causal, scale)
     assert not torch.equal(out16, out.detach())
     # a float64 bias takes the same path and gets a float64 gradient
     b64 = b32.double().requires_grad_()
-    out64 = flash_attention_fn(q, k, v, b64, causal, 0.3)
+    out64 = flash_attention_fn(q, k, v, b64, causal, scale)
     out64.backward(do)
     assert b64.grad.dtype == torch.float64 and torch.equal(out64, out.detach())
     assert torch.equal(b64.grad.float(), bb.grad)
