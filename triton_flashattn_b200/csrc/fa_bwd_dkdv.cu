@@ -518,8 +518,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
               const float2 f = P2::unpack(w[e]);
               const int i = c * 8 + e * 2;
               const f32x2 a = ffma2(f2(f.x, f.y), f2(kLog2e, kLog2e), f2(pr[i], pr[i + 1]));
-              // every fourth pair on the FMA pipe, the rest on the special-function unit
-              const f32x2 pe = (e == 1) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
+              const f32x2 pe = f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
               pr[i] = f2_lo(pe);
               pr[i + 1] = f2_hi(pe);
             }

@@ -416,7 +416,9 @@ __global__ void __launch_bounds__(192, 2) dq_from_ds_kernel(const __grid_constan
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int m_block = gridDim.x - 1 - blockIdx.x;
-  const int bh = blockIdx.y;
+  // the (batch, head) problems in reverse: the dS tiles written last by the dK/dV kernel are
+  // still in L2 when this kernel starts
+  const int bh = gridDim.y - 1 - blockIdx.y;
   const int b = bh / p.H;
   const int h = bh - b * p.H;
   const int m0 = m_block * 128;
