@@ -60,6 +60,7 @@ struct DkdvParams {
   int H, M, N, D;
   int n_nblk, n_tiles;  // key blocks per (batch, head); tiles = n_nblk * B * H
   int causal, bias_vec32, bias_b_mul, bias_h_mul;
+  int dkv_vec32;  // dk / dv bases and strides are multiples of 32 bytes
   int store_ds;    // the 16-bit dS tiles go out through map_dbias (as dbias, or as scratch for dQ)
   int zero_tiles;  // ... and zero tiles go to the causally skipped part (16-bit dbias only)
   float* dbias_f32;  // fp32 bias gradient, written from registers (fp32 bias only), or null
@@ -423,7 +424,10 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
 
     constexpr int BR = BIAS == 1 ? 0 : BK;  // bias staged in registers only for kinds 2 and 3
     BiasRegs<BR> bnext;
-    float lse_next = -INFINITY, delta_next = 0.f;  // -LSE2 and delta of the coming step
+    // LSE2 and delta of the coming step's row, as loaded: they are only looked at (negated,
+    // replaced for rows beyond M) when that step starts, so the loads travel during this one
+    float lse_next = 0.f, delta_next = 0.f;
+    bool row_ok_next = false;
     // fetches bias / -LSE2 / delta of query block `mblk` for the tile (bh_, key column c0)
     auto prefetch = [&](int bh_, int c0, int mblk) {
       const int b_ = bh_ / p.H, h_ = bh_ - b_ * p.H;
@@ -434,9 +438,10 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         load_bias_row<BK>(bnext, p.bias, bias_bh + (int64_t)m * p.bias_sM, row_ok, c0, p.N,
                           p.bias_vec32 != 0);
       }
-      // -LSE2 / delta of the row; rows beyond M get -inf / 0, which makes their P and dS zero
-      lse_next = row_ok ? -__ldcg(p.lse + (int64_t)bh_ * p.M + m) : -INFINITY;
-      delta_next = row_ok ? __ldcg(p.delta + (int64_t)bh_ * p.M + m) : 0.f;
+      const int64_t idx = (int64_t)bh_ * p.M + min(m, p.M - 1);
+      lse_next = __ldcg(p.lse + idx);
+      delta_next = __ldcg(p.delta + idx);
+      row_ok_next = row_ok;
     };
     // Loop state is kept small on purpose (registers): the running step count gs, the tile
     // counter it, and per tile bh, col0 and the current query block mb; the first query block
@@ -473,7 +478,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           load_bias_row<3>(bcur, p.bias, b_ * p.bias_sB + h_ * p.bias_sH + (int64_t)(m0 + r) * p.bias_sM,
                            m0 + r < p.M, col0, p.N, p.bias_vec32 != 0);
         }
-        const float neg_lse = lse_next, delta_r = delta_next;
+        // rows beyond M get -inf / 0, which makes their P and dS zero
+        const float neg_lse = row_ok_next ? -lse_next : -INFINITY, delta_r = row_ok_next ? delta_next : 0.f;
         if (mb + 1 < n_mblk) prefetch(bh, col0, mb + 1);
         // S and "dV of the previous step has read P" are usually true by now: one combined look
         uint32_t ps = 0, pdv = 1, pb = 1;
@@ -672,10 +678,22 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
             for (int i = 0; i < kQD; ++i) a[i] = 0;
           }
           if (n < p.N) {
+            if (p.dkv_vec32 && d0 + kQD <= p.D) {
+              // whole 32-byte sectors per store: half as many transactions as 16-byte stores for
+              // these row-strided writes
 #pragma unroll
-            for (int c = 0; c < kQD / 8; ++c) {
-              const int d = d0 + c * 8;
-              if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, mul);
+              for (int c = 0; c < kQD / 16; ++c) {
+                const uint4 lo = pack8<P2>(a + c * 16, mul), hi = pack8<P2>(a + c * 16 + 8, mul);
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(row + d0 + c * 16),
+                             "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                             : "memory");
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < kQD / 8; ++c) {
+                const int d = d0 + c * 8;
+                if (d < p.D) *reinterpret_cast<uint4*>(row + d) = pack8<P2>(a + c * 8, mul);
+              }
             }
           }
         }
@@ -760,6 +778,10 @@ int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
     return reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || s[0] % 8 || s[1] % 8 || s[2] % 8;
   };
   if (bad(p.dk, p.dk_stride) || bad(p.dv, p.dv_stride)) return FA_ERR_ALIGN;
+  auto al32 = [](const void* ptr, const int64_t s[3]) {
+    return reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && s[0] % 16 == 0 && s[1] % 16 == 0 && s[2] % 16 == 0;
+  };
+  kp.dkv_vec32 = al32(p.dk, p.dk_stride) && al32(p.dv, p.dv_stride);
   kp.bias_b_mul = kp.bias_h_mul = 0;
   kp.map_bias = kp.map_q;
   if (p.bias_kind == FA_BIAS_SAME) {
