@@ -48,6 +48,7 @@ struct FwdParams {
   int64_t o_sB, o_sM, o_sH;
   int H, M, N, D;
   int causal;
+  int o_vec32;  // o's base and strides are multiples of 32 bytes
   int bias_b_mul, bias_h_mul;
   int n_mblk, n_pairs, n_units;  // query blocks / block pairs per (batch, head); units = pairs * B * H
   float sm_scale;
@@ -584,10 +585,22 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
         tmem_ld32(tm_o + c * 32, o);
         tmem_ld_wait();
         if (m < p.M) {
+          if (p.o_vec32 && c * 32 + 32 <= p.D) {
+            // whole 32-byte sectors per store: half as many transactions as 16-byte stores for
+            // these row-strided writes
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int d = c * 32 + q4 * 8;
-            if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + q4 * 8, inv);
+            for (int q2 = 0; q2 < 2; ++q2) {
+              const uint4 lo = pack8<P2>(o + q2 * 16, inv), hi = pack8<P2>(o + q2 * 16 + 8, inv);
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + c * 32 + q2 * 16),
+                           "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                           : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const int d = c * 32 + q4 * 8;
+              if (d < p.D) *reinterpret_cast<uint4*>(orow + d) = pack8<P2>(o + q4 * 8, inv);
+            }
           }
         }
       }
@@ -660,6 +673,8 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
       p.o_stride[2] % 8)
     return FA_ERR_ALIGN;
   fp.o = p.o;
+  fp.o_vec32 = reinterpret_cast<uintptr_t>(p.o) % 32 == 0 && p.o_stride[0] % 16 == 0 && p.o_stride[1] % 16 == 0 &&
+               p.o_stride[2] % 16 == 0;
   fp.lse = p.lse;
   fp.status = status;
   fp.o_sB = p.o_stride[0];
