@@ -2,31 +2,42 @@
 //
 // Persistent kernel, one CTA per SM.  A CTA works on PAIRS of query tiles: two
 // consecutive blocks of 128 query rows of one (batch, head), which share every K / V
-// block they visit.  Roles (352 threads):
+// block they visit.  Roles (384 threads):
 //   warps 0-3   softmax group of tile 0: thread = one query row (= tensor-memory lane)
 //   warps 4-7   softmax group of tile 1
 //   warp 8      TMA producer (one lane): Q pair per unit, K ring (128-key stages), V ring
 //               (64-key half stages)
-//   warp 9      MMA issuer (one lane), tensor-memory owner
+//   warp 9      MMA issuer of tile 0 (one lane), tensor-memory owner
 //   warp 10     TMA producer of the bias / mask ring (one lane); it also asks for the
 //               tiles a few units ahead to be pulled into L2
-// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  Per key block j and tile t:
-//   S_t = Q_t K_j^T           (both operands in shared memory, N = 128)
-//   the row thread reads its 128 scores in two halves of 64 keys; per half it adds the
-//   bias tile (streamed by TMA into a ring of [128 rows][64 keys] units), applies the
-//   masks, updates the running maximum (log2 domain), forms P = exp2(s - m), and writes
-//   the 16-bit P half over the S columns it has already consumed
-//   O_t += P_t[half] V_j[half]   (P is the tensor-memory operand, V MN-major in shared
-//                                  memory), issued per half so that it overlaps the
-//                                  softmax of the other half
-// A row is owned by one thread, so the row maximum and the row sum need no exchange
-// between threads.  While one tile's softmax runs, the tensor core works on the other
-// tile: the issue order is PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1).  All tensor-core work is
-// issued by one thread; products issued by one thread execute in issue order, so
-// S_t(j+1) needs no barrier against PV_t(j), which reads P out of the same columns.
-// The running maximum is only raised when it grows by more than 8 (log2 units); only
-// then is O rescaled (by the row's own thread, after the products into it have finished).
-// Ring stages, tensor-memory buffers and barrier phases run on from unit to unit.
+//   warp 11     MMA issuer of tile 1 (one lane)
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  The 128 score columns of a tile are
+// two halves of 64 that swap roles every key block.  In step c (f = c & 1):
+//   columns [64f, 64f+64)       scores of keys 0-63, read first; afterwards they hold the
+//                               16-bit P of all 128 keys (two halves of 32 columns)
+//   columns [64(1-f), +64)      scores of keys 64-127, read second; once they are in
+//                               registers the columns are free, and the scores of keys 0-63
+//                               of the NEXT block are computed into them while this step's
+//                               second softmax half still runs
+// Per key block j and tile t:
+//   S_t[half] = Q_t K_j[half]^T    (both operands in shared memory, N = 64)
+//   the row thread adds the bias tile (streamed by TMA into a ring of [128 rows][64 keys]
+//   units), applies the masks, updates the running maximum (log2 domain), forms
+//   P = exp2(s - m) and writes the 16-bit P half
+//   O_t += P_t[half] V_j[half]     (P is the tensor-memory operand, V MN-major in shared
+//                                   memory), issued per half
+//   the scores of keys 64-127 of block j+1 go over the columns P_t(j) was read from: same
+//   issuing thread, and products issued by one thread execute in issue order, so no barrier
+//   is needed between them
+// So a softmax group only waits for the tensor core at the start of a unit; the two tiles'
+// products interleave freely on the tensor core.  A row is owned by one thread: the row
+// maximum and the row sum need no exchange between threads.  The running maximum is only
+// raised when it grows by more than 8 (log2 units); only then is O rescaled (by the row's
+// own thread, after the products into it have finished).  Ring stages, tensor-memory
+// buffers and barrier phases run on from unit to unit.  K / V ring stages are handed back
+// by both issuers (their "empty" barriers count two arrivals); an issuer whose tile does
+// not visit a block still waits for its loads and hands the stages back, so that every
+// waiter sees every completion of a barrier it waits on.
 //
 // Replaces _attn_fwd / _attn_fwd_inner of the reference (flash_attention.py
 // lines 12-194): same masks (bounds, top-left causal, bool, additive float
@@ -55,7 +66,7 @@ struct FwdParams {
 };
 
 enum FwdSite { kSiteQFull = 1, kSiteQEmpty, kSiteKFull, kSiteKEmpty, kSiteVFull, kSiteVEmpty,
-               kSiteSFull, kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue };
+               kSiteSFull, kSiteSRead, kSitePFull, kSitePvDone, kSiteBiasFull, kSiteBiasEmpty, kSiteEpilogue };
 
 template <int DP, int BIAS>
 struct FwdSmem {
@@ -154,7 +165,7 @@ struct BiasWalk {
 };
 
 template <int DP, typename T, int BIAS>
-__global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using L = FwdSmem<DP, BIAS>;
   using P2 = Pack2<T>;
   constexpr int KB = DP / 64;     // 64-column blocks per Q / K / V tile
@@ -169,7 +180,7 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[3], v_empty[3];
-  __shared__ uint64_t s_full[2], p_full[2][2], pv_done[2][2];
+  __shared__ uint64_t s_full[2][2], s_read[2], p_full[2][2], pv_done[2][2];
   __shared__ uint64_t bias_full[2][3], bias_empty[3];  // full: one set per consuming group
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -183,19 +194,20 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
-    mbar_init(&q_empty, 1);
+    mbar_init(&q_empty, 2);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&s_full[i], 1);
+      mbar_init(&k_empty[i], 2);
+      mbar_init(&s_read[i], 4);
       for (int h = 0; h < 2; ++h) {
+        mbar_init(&s_full[i][h], 1);
         mbar_init(&p_full[i][h], 4);
         mbar_init(&pv_done[i][h], 1);
       }
     }
     for (int i = 0; i < 3; ++i) {
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
       mbar_init(&bias_full[0][i], 1);
       mbar_init(&bias_full[1][i], 1);
       mbar_init(&bias_empty[i], 4);
@@ -255,72 +267,86 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
         }
       }
     }
-  } else if (warp == 9) {
-    // --------------------------------------------------------------- MMA issuer
+  } else if (warp == 9 || warp == 11) {
+    // ------------------------------------------- MMA issuer of tile slot t (one lane)
     if (lane == 0 && live) {
+      const int t = warp == 9 ? 0 : 1;
       constexpr bool bf = P2::kIsBf16;
-      constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 128);
+      constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 64);
       constexpr uint32_t idesc_pv = make_idesc(bf, false, true, 128, DP);
-      const uint32_t q_addr = smem_u32(smem + L::kQ), k_addr = smem_u32(smem + L::kK);
+      const uint32_t q_addr = smem_u32(smem + L::kQ) + t * L::kQTile, k_addr = smem_u32(smem + L::kK);
       const uint32_t v_addr = smem_u32(smem + L::kV);
+      const uint32_t tm_s = tmem + t * 128, tm_o = tmem + 256 + t * 128;
       bool ok = true;
-      uint32_t cs[2] = {0, 0};  // steps done per tile slot, over all units
+      uint32_t cs = 0;          // steps done by this tile slot, over all units
       uint32_t gk = 0, gv = 0;  // key blocks / V halves consumed before this unit
       Unit u;
-      auto issue_qk = [&](int t, uint32_t kslot) {
-        issue_gemm_ss<KS_QK, false, false>(tmem + t * 128, make_sdesc(q_addr + t * L::kQTile, 0, 1024),
-                                           make_sdesc(k_addr + kslot * L::kKStage, 0, 1024), kBlk, kBlk,
-                                           idesc_qk, false);
-        mma_commit(&s_full[t]);
+      // scores of one 64-key half of the block in ring stage `kslot` -> column half `ch`
+      auto issue_qk = [&](uint32_t kslot, int keys, uint32_t ch) {
+        issue_gemm_ss<KS_QK, false, false>(tm_s + ch * 64, make_sdesc(q_addr, 0, 1024),
+                                           make_sdesc(k_addr + kslot * L::kKStage + keys * (64 * 128), 0, 1024),
+                                           kBlk, kBlk, idesc_qk, false);
+        mma_commit(&s_full[t][keys]);
       };
       for (int it = 0; ok && unit_at(p, it, u); ++it) {
         if (u.nmax == 0) continue;
-        // ---- first scores of both tiles
+        const int nblk = u.nb(t);
         ok = mbar_wait(&q_full, it & 1, ctx, kSiteQFull, it);
         if (ok) ok = mbar_wait(&k_full[gk & 1], (gk >> 1) & 1, ctx, kSiteKFull, 0);
         if (!ok) break;
         tc_fence_after();
-        for (int t = 0; t < 2; ++t)
-          if (u.nb(t) > 0) issue_qk(t, gk & 1);
+        if (nblk > 0) {
+          issue_qk(gk & 1, 0, cs & 1);
+          issue_qk(gk & 1, 1, (cs & 1) ^ 1);
+        }
         mma_commit(&k_empty[gk & 1]);
         if (u.nmax == 1) mma_commit(&q_empty);
         for (int j = 0; j < u.nmax && ok; ++j) {
           const uint32_t kn = (gk + j + 1) & 1, kn_par = ((gk + j + 1) >> 1) & 1;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (j >= u.nb(t)) continue;
-            const bool last_user = t == 1 || j >= u.nb1;  // tile 1 comes second when it visits j
-            // looked at early: the answers arrive while this thread waits for P
-            uint32_t pk = 1;
-            if (j + 1 < u.nb(t)) pk = mbar_poll(&k_full[kn], kn_par);
-            for (int h = 0; h < 2 && ok; ++h) {
-              const uint32_t gh = gv + 2 * j + h;
-              const uint32_t vs = gh % VS, v_par = (gh / VS) & 1;
+          const bool more = j + 1 < u.nmax;  // the unit has a block j+1 (this tile may not visit it)
+          const bool mine = j < nblk, mine_next = j + 1 < nblk;
+          const uint32_t f = cs & 1;  // column half that holds keys 0-63 of this step, and P
+          for (int h = 0; h < 2 && ok; ++h) {
+            const uint32_t gh = gv + 2 * j + h;
+            const uint32_t vs = gh % VS, v_par = (gh / VS) & 1;
+            if (mine) {
               const uint32_t pv = mbar_poll(&v_full[vs], v_par);
-              ok = mbar_wait_hot(&p_full[t][h], cs[t] & 1, ctx, kSitePFull, j);
+              ok = mbar_wait_hot(&p_full[t][h], cs & 1, ctx, kSitePFull, j);
               if (ok) ok = wait_polled(pv, &v_full[vs], v_par, ctx, kSiteVFull, j);
               if (!ok) break;
               tc_fence_after();
-              issue_gemm_ts<4, true>(tmem + 256 + t * 128, tmem + t * 128 + h * 32,
+              issue_gemm_ts<4, true>(tm_o, tm_s + f * 64 + h * 32,
                                      make_sdesc(v_addr + vs * L::kVHalf, kVBlk, 1024), kVBlk, idesc_pv,
                                      j > 0 || h > 0);
               mma_commit(&pv_done[t][h]);
-              if (last_user) mma_commit(&v_empty[vs]);
-            }
-            if (!ok) break;
-            ++cs[t];
-            if (j + 1 < u.nb(t)) {
-              // S_t(j+1) goes over the columns P_t(j) is read from: same issuing thread, so it
-              // executes after the products just issued
-              ok = wait_polled(pk, &k_full[kn], kn_par, ctx, kSiteKFull, j + 1);
+            } else {
+              // a block only the other tile visits: keep the ring counters in step
+              ok = mbar_wait(&v_full[vs], v_par, ctx, kSiteVFull, j);
               if (!ok) break;
-              tc_fence_after();
-              issue_qk(t, kn);
-              if (t == 1 || j + 1 >= u.nb1) {
+            }
+            mma_commit(&v_empty[vs]);
+            if (h == 0) {
+              // Keys 0-63 of block j+1 go into the column half whose scores (keys 64-127 of
+              // block j) the row threads have just taken into registers: this product runs
+              // under the second half of this step's softmax.
+              if (mine) ok = mbar_wait_hot(&s_read[t], cs & 1, ctx, kSiteSRead, j);
+              if (ok && more) ok = mbar_wait(&k_full[kn], kn_par, ctx, kSiteKFull, j + 1);
+              if (!ok) break;
+              if (mine_next) {
+                tc_fence_after();
+                issue_qk(kn, 0, f ^ 1);
+              }
+            } else {
+              // Keys 64-127 of block j+1 go over the columns P of block j is read from: same
+              // issuing thread, so it executes after the products just issued.
+              if (mine_next) issue_qk(kn, 1, f);
+              if (more) {
                 mma_commit(&k_empty[kn]);
                 if (j + 2 >= u.nmax) mma_commit(&q_empty);
               }
             }
           }
+          if (mine) ++cs;
         }
         gk += u.nmax;
         gv += 2 * u.nmax;
@@ -393,19 +419,27 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
         const int both = (j < u.nb0 ? 1 : 0) + (j < u.nb1 ? 1 : 0);
         if (j < nblk) {
           const uint32_t first = bu + ((t == 1 && j < u.nb0) ? kU : 0);
-          ok = wait_warp(&s_full[t], cs & 1, ctx, kSiteSFull, j);
-          if (!ok) break;
-          tc_fence_after();
+          const uint32_t f = cs & 1;  // column half of keys 0-63 in this step (and of P)
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
+            ok = wait_warp(&s_full[t][h], cs & 1, ctx, kSiteSFull, j);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tm_sh = tm_s + ((static_cast<uint32_t>(h) ^ f) << 6);
             const uint32_t unit = first + h * kUH;
             uint32_t bs = unit % NB, b_par = (b_phase >> bs) & 1;
             uint32_t pbias = 1;
             if (BIAS != 0 && (BIAS != 2 || h == 0)) pbias = mbar_poll(&bias_full[t][bs], b_par);
             float s[64];
-            tmem_ld32(tm_s + h * 64, reinterpret_cast<uint32_t*>(s));
-            tmem_ld32(tm_s + h * 64 + 32, reinterpret_cast<uint32_t*>(s) + 32);
+            tmem_ld32(tm_sh, reinterpret_cast<uint32_t*>(s));
+            tmem_ld32(tm_sh + 32, reinterpret_cast<uint32_t*>(s) + 32);
             tmem_ld_wait();
+            if (h == 1) {
+              // these columns are free: the first half of the next block's scores may land there
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&s_read[t]);
+            }
             const int n0 = j * 128 + h * 64;  // first key of this half
             // ---- score in the natural domain: q.k * sm_scale (+ bias), -inf where masked.
             // Without a bias (and a positive scale) the raw q.k is kept and the scale is
@@ -555,8 +589,8 @@ __global__ void __launch_bounds__(352, 1) fwd_kernel(const __grid_constant__ Fwd
               pk[i + 1] = P2::pack(p2, p3);
             }
             l += (f2_lo(sum01) + f2_hi(sum01)) + (f2_lo(sum23) + f2_hi(sum23));
-            // P (16 bit) over S columns this thread has already read: 64 keys -> 32 columns
-            tmem_st32(tm_s + h * 32, pk);
+            // P (16 bit) over the score columns of keys 0-63, which this thread has read
+            tmem_st32(tm_s + f * 64 + h * 32, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -629,7 +663,7 @@ int launch_inst(const FwdParams& fp, dim3 grid, cudaStream_t stream) {
       return FA_ERR_CUDA;
     configured[dev] = true;
   }
-  return launch_overlapped(kern, grid, 352, L::kDynamic, stream, fp);
+  return launch_overlapped(kern, grid, 384, L::kDynamic, stream, fp);
 }
 
 template <int DP, typename T>
