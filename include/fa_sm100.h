@@ -43,7 +43,8 @@ enum fa_error {
   FA_ERR_ALIGN = 5,       /* a base pointer or stride breaks the 16-byte rule   */
   FA_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed                  */
   FA_ERR_DEVICE_WAIT = 7, /* a kernel gave up a bounded wait (see fa_last_device_status) */
-  FA_ERR_UNSUPPORTED = 8, /* legal in the reference, not built in this library  */
+  FA_ERR_UNSUPPORTED = 8, /* legal in the reference, not built in this library
+                             (no input reaches it today: every head dim of FA:776 runs) */
   FA_ERR_TOO_LARGE = 9    /* a size exceeds a stated limit of the entry point   */
 };
 
@@ -57,7 +58,8 @@ enum fa_error {
  *                  element type (16-bit for FA_BIAS_SAME, fp32 for FA_BIAS_F32).  With
  *                  FA_BIAS_F32 and causal = 1 the caller zero-fills dbias first: tiles
  *                  above the diagonal are not visited (with FA_BIAS_SAME the library
- *                  writes those zeros itself)
+ *                  writes those zeros itself, except at D = 256, where the caller
+ *                  zero-fills a causal dbias of either type)
  *   lse, delta   : (B, H, M) fp32, contiguous
  * Alignment: q/k/v/do base pointers and strides*2 bytes are multiples of 16; the
  * same holds for bias/dbias strides in bytes (the Python layer pads when a row
@@ -97,11 +99,12 @@ typedef struct fa_params {
   int64_t bias_stride[3];
   int64_t dbias_stride[3];
 
-  /* Backward with FA_BIAS_F32 only (required there, ignored otherwise): a (B,H,M,N) scratch
-   * tensor in q's 16-bit dtype.  The dK/dV stage leaves dS there for the dQ stage (which
-   * consumes dS as a 16-bit tensor-core operand, exactly as the reference rounds dS before
-   * its dQ product, FA:517).  Same stride rules as dbias.  Contents afterwards: dS rounded to
-   * 16 bits at and below the causal diagonal, unspecified above it. */
+  /* Backward with FA_BIAS_F32, and every backward at D = 256 except the one that writes a
+   * 16-bit dbias (FA_BIAS_SAME with write_dbias = 1): a (B,H,M,N) scratch tensor in q's 16-bit
+   * dtype, required in those cases, ignored otherwise.  The dK/dV stage leaves dS there for
+   * the dQ stage (which consumes dS as a 16-bit tensor-core operand, exactly as the reference
+   * rounds dS before its dQ product, FA:517).  Same stride rules as dbias.  Contents
+   * afterwards: dS rounded to 16 bits at and below the causal diagonal, unspecified above it. */
   void* ds16;
   int64_t ds16_stride[3];
 } fa_params;

@@ -55,6 +55,59 @@ def test_ragged_lengths(M, N, causal, bias_kind, device_ok):
     check_case(1, M, N, 2, 64, HF, bias_kind, causal, seed=2)
 
 
+@pytest.mark.parametrize("dtype", [BF, HF])
+@pytest.mark.parametrize("M,N,causal", [(256, 256, False), (256, 256, True), (200, 136, False), (300, 100, True),
+                                        (100, 300, True), (129, 1, False), (640, 512, True)])
+@pytest.mark.parametrize("bias_kind,trainable", [(None, False), ("float", True), ("float", False), ("bool", False)])
+def test_head_dim_256(dtype, M, N, causal, bias_kind, trainable, device_ok):
+    """Head dimension 256 (flash_attention.py line 776 accepts it): one query tile per CTA in the
+    forward, the transposed 64-key dK/dV kernel and the streamed dQ in the backward.
+
+    delta = rowsum(o * do) is formed from the 16-bit output, and two correct 16-bit roundings of
+    o differ by one unit in some of a row's elements; that difference, summed over D = 256
+    products, enters dS = P (dP - delta) in full where P is near 1 (about 1.4x the D = 128
+    figure).  So against the oracle fed its OWN rounded output the bf16 bound is taken 1.5x;
+    against the oracle fed this library's saved output the plain rule must hold.  (The
+    reference's own Triton kernels on the same inputs: dbias max-abs 5e-2 to 6e-2, 14 to 52
+    elements over 2e-2; this library 2.5e-2 to 3.2e-2, 1 to 13 elements.)"""
+    q, k, v, bias, do = make_inputs(2, M, N, 2, 256, dtype, bias_kind, 12)
+    ours = run_ours(q, k, v, bias, causal, None, do, trainable)
+    label = f"D256 M{M} N{N} {dtype} bias={bias_kind} trainable={trainable} causal={causal}: "
+    compare(ours, q, k, v, bias, causal, None, do, dtype, 1.5 if dtype == BF else 1.0, label)
+    ref_saved = oracle.attention_backward(q, k, v, bias, causal, None, do, o_saved=ours["out"])
+    for n, t in ours.items():
+        accept(n, account(t, ref_saved[n], dtype), dtype, label=label + "(saved output) ")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_dim_256_fp32_bias_and_packed_qkv(causal, device_ok):
+    from triton_flashattn_b200 import flash_attention_fn, flash_attention_qkvpacked_fn
+
+    B, S, H, D = 2, 200, 2, 256
+    g = torch.Generator().manual_seed(13)
+    qkv = torch.randn(B, S, 3, H, D, generator=g).to(BF).cuda()
+    b32 = torch.randn(B, H, S, S, generator=g).cuda()
+    do = torch.randn(B, S, H, D, generator=g).to(BF).cuda()
+    qkv_g, bb = qkv.clone().requires_grad_(), b32.clone().requires_grad_()
+    out = flash_attention_qkvpacked_fn(qkv_g, bb, causal)
+    out.backward(do)
+    q, k, v = (qkv[:, :, i] for i in range(3))
+    ref = oracle.attention_backward(q, k, v, b32, causal, None, do)
+    assert bb.grad.dtype == torch.float32 and qkv_g.grad.shape == qkv.shape
+    ours = {"out": out.detach(), "dq": qkv_g.grad[:, :, 0], "dk": qkv_g.grad[:, :, 1], "dv": qkv_g.grad[:, :, 2],
+            "dbias": bb.grad}
+    for n, t in ours.items():
+        accept(n, account(t, ref[n], BF), BF, label=f"D256 packed fp32 bias causal={causal} {n}: ")
+    if causal:
+        assert torch.all(bb.grad[0, 0].triu(1) == 0)
+    # the unpacked entry on the same data gives the same bits
+    qq, kk, vv = (t.clone().contiguous().requires_grad_() for t in (q, k, v))
+    out2 = flash_attention_fn(qq, kk, vv, b32, causal)
+    out2.backward(do)
+    assert torch.equal(out2, out.detach()) and torch.equal(qq.grad, qkv_g.grad[:, :, 0])
+    assert torch.equal(kk.grad, qkv_g.grad[:, :, 1]) and torch.equal(vv.grad, qkv_g.grad[:, :, 2])
+
+
 @pytest.mark.parametrize("D", [16, 32])
 @pytest.mark.parametrize("bias_kind", [None, "float"])
 def test_small_head_dims(D, bias_kind, device_ok):

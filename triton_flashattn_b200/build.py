@@ -26,6 +26,7 @@ SOURCES = [
     "fa_bwd_pre.cu",
     "fa_bwd_dkdv.cu",
     "fa_bwd_dq.cu",
+    "fa_bwd_dkdv256.cu",
     "fa_bwd_static.cu",
 ]
 

@@ -141,7 +141,6 @@ int validate_common(const fa_params* p) {
   if (p->struct_size != sizeof(fa_params)) return FA_ERR_ABI;
   if (p->B < 1 || p->H < 1 || p->M < 1 || p->N < 1) return FA_ERR_SHAPE;
   if (!(p->D == 16 || p->D == 32 || p->D == 64 || p->D == 128 || p->D == 256)) return FA_ERR_SHAPE;
-  if (p->D == 256) return FA_ERR_UNSUPPORTED;
   if (p->dtype != FA_F16 && p->dtype != FA_BF16) return FA_ERR_DTYPE;
   if (p->bias_kind < FA_BIAS_NONE || p->bias_kind > FA_BIAS_F32) return FA_ERR_DTYPE;
   if (!p->q || !p->k || !p->v || !p->o || !p->lse) return FA_ERR_NULL;
@@ -159,6 +158,8 @@ int validate_bwd(const fa_params* p) {
     if (!p->dbias) return FA_ERR_NULL;
   }
   if (p->bias_kind == FA_BIAS_F32 && !p->ds16) return FA_ERR_NULL;
+  // head dim 256: dQ is always the streamed product over the 16-bit dS
+  if (p->D == 256 && !(p->write_dbias && p->bias_kind == FA_BIAS_SAME) && !p->ds16) return FA_ERR_NULL;
   return FA_OK;
 }
 
@@ -192,7 +193,7 @@ const char* fa_status_string(int code) {
     case FA_ERR_ALIGN: return "pointer or stride is not a multiple of 16 bytes";
     case FA_ERR_CUDA: return "a CUDA call failed";
     case FA_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait";
-    case FA_ERR_UNSUPPORTED: return "not supported by this build (head dim 256)";
+    case FA_ERR_UNSUPPORTED: return "not supported by this build";
     case FA_ERR_TOO_LARGE: return "size exceeds a limit of this entry point";
     default: return "unknown error code";
   }

@@ -739,6 +739,7 @@ int launch_bias(const DkdvParams& kp, int bias_kind, dim3 grid, cudaStream_t str
 
 
 int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status) {
+  if (p.D == 256) return launch_bwd_dkdv_d256(p, stream, status);
   DkdvParams kp;
   int r = make_tmap_bshd(&kp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
   if (r) return r;

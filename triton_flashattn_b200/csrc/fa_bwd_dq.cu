@@ -565,9 +565,15 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   // When the dK/dV stage has just left dS in a 16-bit tensor (the bias gradient itself, or the
   // scratch an fp32 bias comes with) the streamed GEMM variant is used, otherwise the general
   // kernel.
+  // At head dimension 256 only the streamed variant exists: its dK/dV kernel always leaves dS.
   const bool f32 = p.bias_kind == FA_BIAS_F32;
+  const bool d256 = p.D == 256;
   if (f32 && !p.ds16) return FA_ERR_NULL;
-  const bool from_ds = f32 || (p.write_dbias && p.bias_kind == FA_BIAS_SAME);
+  const bool from_ds = d256 || f32 || (p.write_dbias && p.bias_kind == FA_BIAS_SAME);
+  const int64_t* ds_stride = f32 ? p.ds16_stride : p.dbias_stride;
+  const void* ds = f32 ? p.ds16 : p.dbias;
+  if (d256) ds = d256_ds_tensor(p, &ds_stride);
+  if (from_ds && !ds) return FA_ERR_NULL;
   int r = make_tmap_bshd(&kp.map_q, p.q, p.B, p.M, p.H, p.D, p.q_stride, 128);
   if (r) return r;
   r = make_tmap_bshd(&kp.map_k, p.k, p.B, p.N, p.H, p.D, p.k_stride, from_ds ? 64 : 128);
@@ -578,8 +584,7 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   if (r) return r;
   if (from_ds) {
     int bm, hm;
-    r = make_tmap_bhmn(&kp.map_ds, f32 ? p.ds16 : p.dbias, 2, p.B, p.H, p.M, p.N,
-                       f32 ? p.ds16_stride : p.dbias_stride, 64, 128, &bm, &hm);
+    r = make_tmap_bhmn(&kp.map_ds, ds, 2, p.B, p.H, p.M, p.N, ds_stride, 64, 128, &bm, &hm);
     if (r) return r;
     if (!bm || !hm) return FA_ERR_ALIGN;
   } else {
@@ -588,7 +593,7 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   if (reinterpret_cast<uintptr_t>(p.dq) % 16 != 0 || p.dq_stride[0] % 8 || p.dq_stride[1] % 8 ||
       p.dq_stride[2] % 8)
     return FA_ERR_ALIGN;
-  if (p.bias_kind != FA_BIAS_NONE && !f32) {
+  if (p.bias_kind != FA_BIAS_NONE && !from_ds) {
     const int eb = p.bias_kind == FA_BIAS_BOOL ? 1 : 2;
     if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || (p.bias_stride[0] * eb) % 16 ||
         (p.bias_stride[1] * eb) % 16 || (p.bias_stride[2] * eb) % 16)
@@ -622,6 +627,9 @@ int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status) {
   kp.n_tiles = kp.n_mblk * p.B * p.H;
   const dim3 grid((p.M + 127) / 128, p.B * p.H);  // streamed-dS variant: one CTA per tile
   const int dp = padded_head_dim(p.D);
+  if (dp == 256)
+    return p.dtype == FA_BF16 ? launch_from_ds<256, __nv_bfloat16>(kp, grid, stream)
+                              : launch_from_ds<256, __half>(kp, grid, stream);
   if (p.dtype == FA_BF16) {
     return dp == 64 ? launch_bias<64, __nv_bfloat16>(kp, p.bias_kind, from_ds, grid, stream)
                     : launch_bias<128, __nv_bfloat16>(kp, p.bias_kind, from_ds, grid, stream);

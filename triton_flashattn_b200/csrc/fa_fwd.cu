@@ -62,6 +62,7 @@ struct FwdParams {
   int o_vec32;  // o's base and strides are multiples of 32 bytes
   int bias_b_mul, bias_h_mul;
   int n_mblk, n_pairs, n_units;  // query blocks / block pairs per (batch, head); units = pairs * B * H
+  int tiles;                     // query tiles per unit: 2, or 1 at head dim 256
   float sm_scale;
 };
 
@@ -73,11 +74,14 @@ struct FwdSmem {
   static constexpr int kQTile = 128 * DP * 2;   // one query tile
   static constexpr int kKStage = 128 * DP * 2;  // 128 keys
   static constexpr int kVHalf = 64 * DP * 2;    // 64 keys
-  static constexpr int kKStages = 2;
-  static constexpr int kVStages = 3;
-  static constexpr int kBiasStages = BIAS == 0 ? 0 : 3;  // 16 KB units
+  // Head dim 256: one query tile per unit, single K stage, two V half stages, two bias units
+  // (64 + 64 + 64 + 32 KB); otherwise two tiles, 2 / 3 / 3 stages (64 + 64 + 48 + 48 KB at 128).
+  static constexpr int kTiles = DP == 256 ? 1 : 2;
+  static constexpr int kKStages = DP == 256 ? 1 : 2;
+  static constexpr int kVStages = DP == 256 ? 2 : 3;
+  static constexpr int kBiasStages = BIAS == 0 ? 0 : (DP == 256 ? 2 : 3);  // 16 KB units
   static constexpr int kQ = 0;
-  static constexpr int kK = kQ + 2 * kQTile;
+  static constexpr int kK = kQ + kTiles * kQTile;
   static constexpr int kV = kK + kKStages * kKStage;
   static constexpr int kBias = kV + kVStages * kVHalf;
   static constexpr int kTotal = kBias + kBiasStages * kBlk;
@@ -102,10 +106,10 @@ __device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
   u.bh = k / p.n_pairs;
   const int pos = k - u.bh * p.n_pairs;
   const int pair = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_pairs - 1 - (pos >> 1)) : pos;
-  u.mb0 = pair * 2;
+  u.mb0 = pair * p.tiles;
   const int nblk_all = (p.N + 127) >> 7;
   u.nb0 = u.mb0 >= p.n_mblk ? 0 : (p.causal ? min(nblk_all, u.mb0 + 1) : nblk_all);
-  u.nb1 = u.mb0 + 1 >= p.n_mblk ? 0 : (p.causal ? min(nblk_all, u.mb0 + 2) : nblk_all);
+  u.nb1 = (p.tiles < 2 || u.mb0 + 1 >= p.n_mblk) ? 0 : (p.causal ? min(nblk_all, u.mb0 + 2) : nblk_all);
   u.nmax = max(u.nb0, u.nb1);
   return true;
 }
@@ -172,6 +176,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
   constexpr int KS_QK = DP / 16;  // MMA K slices of Q K^T
   constexpr uint32_t NB = L::kBiasStages > 0 ? L::kBiasStages : 1;
   constexpr uint32_t VS = L::kVStages;
+  constexpr uint32_t KST = L::kKStages;
   constexpr uint32_t kTmemCols = 512;
   constexpr int kVBlk = 64 * 128;  // bytes of one [64 keys][64] block of a V half stage
   constexpr int kPf = 4;           // bias units asked into L2 ahead of the shared-memory ring
@@ -179,7 +184,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[3], v_empty[3];
+  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[3], v_empty[3];  // rings: up to 2 / 3 stages
   __shared__ uint64_t s_full[2][2], s_read[2], p_full[2][2], pv_done[2][2];
   __shared__ uint64_t bias_full[2][3], bias_empty[3];  // full: one set per consuming group
   __shared__ uint32_t tmem_slot;
@@ -241,15 +246,15 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
         // the Q pair is free once every Q K^T product of the previous unit is through
         if (it >= 1) ok = mbar_wait(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&q_full, 2 * L::kQTile);
-        for (int t = 0; t < 2; ++t)
+        mbar_expect_tx(&q_full, L::kTiles * L::kQTile);
+        for (int t = 0; t < L::kTiles; ++t)
           for (int kb = 0; kb < KB; ++kb)
             tma_load_4d(smem + L::kQ + t * L::kQTile + kb * kBlk, &p.map_q, &q_full, kb * 64, h,
                         (u.mb0 + t) * 128, b);
         for (int j = 0; j < u.nmax && ok; ++j, ++gk) {
-          const int ks = gk & 1;
+          const uint32_t ks = gk % KST;
           const int n0 = j * 128;
-          if (gk >= 2) ok = mbar_wait(&k_empty[ks], ((gk >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+          if (gk >= KST) ok = mbar_wait(&k_empty[ks], (gk / KST - 1) & 1, ctx, kSiteKEmpty, j);
           if (!ok) break;
           mbar_expect_tx(&k_full[ks], L::kKStage);
           for (int kb = 0; kb < KB; ++kb)
@@ -292,17 +297,17 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
         if (u.nmax == 0) continue;
         const int nblk = u.nb(t);
         ok = mbar_wait(&q_full, it & 1, ctx, kSiteQFull, it);
-        if (ok) ok = mbar_wait(&k_full[gk & 1], (gk >> 1) & 1, ctx, kSiteKFull, 0);
+        if (ok) ok = mbar_wait(&k_full[gk % KST], (gk / KST) & 1, ctx, kSiteKFull, 0);
         if (!ok) break;
         tc_fence_after();
         if (nblk > 0) {
-          issue_qk(gk & 1, 0, cs & 1);
-          issue_qk(gk & 1, 1, (cs & 1) ^ 1);
+          issue_qk(gk % KST, 0, cs & 1);
+          issue_qk(gk % KST, 1, (cs & 1) ^ 1);
         }
-        mma_commit(&k_empty[gk & 1]);
+        mma_commit(&k_empty[gk % KST]);
         if (u.nmax == 1) mma_commit(&q_empty);
         for (int j = 0; j < u.nmax && ok; ++j) {
-          const uint32_t kn = (gk + j + 1) & 1, kn_par = ((gk + j + 1) >> 1) & 1;
+          const uint32_t kn = (gk + j + 1) % KST, kn_par = ((gk + j + 1) / KST) & 1;
           const bool more = j + 1 < u.nmax;  // the unit has a block j+1 (this tile may not visit it)
           const bool mine = j < nblk, mine_next = j + 1 < nblk;
           const uint32_t f = cs & 1;  // column half that holds keys 0-63 of this step, and P
@@ -721,16 +726,19 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   fp.causal = p.causal ? 1 : 0;
   fp.sm_scale = p.sm_scale;
   fp.n_mblk = (p.M + 127) / 128;
-  fp.n_pairs = (fp.n_mblk + 1) / 2;
+  const int dp = padded_head_dim(p.D);
+  fp.tiles = dp == 256 ? 1 : 2;
+  fp.n_pairs = (fp.n_mblk + fp.tiles - 1) / fp.tiles;
   fp.n_units = fp.n_pairs * p.B * p.H;
   const dim3 grid(persistent_grid(p.causal ? (fp.n_units + 1) / 2 : fp.n_units));
-  const int dp = padded_head_dim(p.D);
   if (p.dtype == FA_BF16) {
-    return dp == 64 ? launch_bias<64, __nv_bfloat16>(fp, p.bias_kind, grid, stream)
-                    : launch_bias<128, __nv_bfloat16>(fp, p.bias_kind, grid, stream);
+    return dp == 64    ? launch_bias<64, __nv_bfloat16>(fp, p.bias_kind, grid, stream)
+           : dp == 128 ? launch_bias<128, __nv_bfloat16>(fp, p.bias_kind, grid, stream)
+                       : launch_bias<256, __nv_bfloat16>(fp, p.bias_kind, grid, stream);
   }
-  return dp == 64 ? launch_bias<64, __half>(fp, p.bias_kind, grid, stream)
-                  : launch_bias<128, __half>(fp, p.bias_kind, grid, stream);
+  return dp == 64    ? launch_bias<64, __half>(fp, p.bias_kind, grid, stream)
+         : dp == 128 ? launch_bias<128, __half>(fp, p.bias_kind, grid, stream)
+                     : launch_bias<256, __half>(fp, p.bias_kind, grid, stream);
 }
 
 }  // namespace fa

@@ -31,6 +31,11 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status);
 int launch_bwd_pre(const fa_params& p, cudaStream_t stream, int* status);
 int launch_bwd_dkdv(const fa_params& p, cudaStream_t stream, int* status);
 int launch_bwd_dq(const fa_params& p, cudaStream_t stream, int* status);
+// Head dimension 256: its own dK/dV kernel, which always leaves the 16-bit dS in global
+// memory (in dbias for a 16-bit bias that wants its gradient, else in the ds16 scratch);
+// d256_ds_tensor names that tensor, the dQ stage streams it.
+int launch_bwd_dkdv_d256(const fa_params& p, cudaStream_t stream, int* status);
+const void* d256_ds_tensor(const fa_params& p, const int64_t** stride);
 int launch_selftest(int mode, int dtype, const void* a, const void* b, void* c, cudaStream_t stream,
                     int* status);
 int launch_selftest_timeout(uint32_t limit_us, cudaStream_t stream, int* status);
@@ -63,7 +68,7 @@ inline int launch_overlapped(Kern kern, dim3 grid, int threads, size_t smem, cud
   return FA_OK;
 }
 
-// Head dims are computed on a padded width: 16/32/64 -> 64, 128 -> 128.
+// Head dims are computed on a padded width: 16/32/64 -> 64, 128 -> 128, 256 -> 256.
 inline int padded_head_dim(int d) { return d <= 64 ? 64 : d; }
 
 // Tile map for a (B, S, H, D) tensor: dims {D, H, S, B}, box {64, 1, rows, 1}.

@@ -89,8 +89,6 @@ def _check_inputs(q, k, v, bias):
     Bk, N, Hk, Dk = k.shape
     assert D == Dk, "q and k must share the head dimension"
     assert D in _HEAD_DIMS, "head dimension must be one of 16, 32, 64, 128, 256"
-    if D == 256:
-        raise NotImplementedError("head dimension 256 is not built yet")
     if v.shape != k.shape:
         raise ValueError("v must have the shape of k (value head dim == query/key head dim)")
     if (Bk, Hk) != (B, H):
@@ -177,9 +175,10 @@ def _flash_attn_bwd(do, q, k, v, o, bias, causal, sm_scale, lse, dq, dk, dv, dbi
     if dbias is not None:
         p.write_dbias = 1
         p.dbias, p.dbias_stride = dbias.data_ptr(), _stride3(dbias)
-    if kind == _cabi.FA_BIAS_F32:
-        # the dK/dV stage hands dS to the dQ stage through a 16-bit scratch tensor
-        ds16 = _empty_dbias(bias, q.dtype)
+    if kind == _cabi.FA_BIAS_F32 or (D == 256 and not (dbias is not None and kind == _cabi.FA_BIAS_SAME)):
+        # the dK/dV stage hands dS to the dQ stage through a 16-bit scratch tensor (fp32 bias; at
+        # head dim 256 always, unless the 16-bit bias gradient itself is that tensor)
+        ds16 = _pitched_empty((B, H, M, N), q.dtype, q.device)
         p.ds16, p.ds16_stride = ds16.data_ptr(), _stride3(ds16)
     _cabi.check(_cabi.load().fa_bwd(ctypes.byref(p), _stream(q)), "fa_bwd")
 
@@ -190,18 +189,26 @@ def _empty_dbias(bias: torch.Tensor, dtype: torch.dtype, zero: bool = False) -> 
     zero fill is needed: the dK/dV kernel writes every tile, including the causally skipped
     ones (the reference relies on zeros_like, FA:799).  `zero`: fp32 gradient of a causal
     problem, whose skipped tiles nobody writes."""
-    B, H, M, N = bias.shape
+    return _pitched_empty(tuple(bias.shape), dtype, bias.device, zero)
+
+
+def _pitched_empty(shape, dtype: torch.dtype, device, zero: bool = False) -> torch.Tensor:
+    """(B, H, M, N) tensor whose row pitch is a multiple of 16 bytes (a view of a padded buffer
+    when N needs it)."""
+    B, H, M, N = shape
     per16 = 16 // dtype.itemsize
     n_pad = (N + per16 - 1) // per16 * per16
     make = torch.zeros if zero else torch.empty
-    buf = make((B, H, M, n_pad), dtype=dtype, device=bias.device)
+    buf = make((B, H, M, n_pad), dtype=dtype, device=device)
     return buf[..., :N]
 
 
 def _new_dbias(bias: torch.Tensor, q: torch.Tensor, causal: bool) -> torch.Tensor:
-    """Gradient buffer for `bias` as the kernels write it: q's dtype when the bias has it, else fp32."""
+    """Gradient buffer for `bias` as the kernels write it: q's dtype when the bias has it, else
+    fp32.  Zero-filled where the kernels skip the causally masked tiles without writing them
+    (fp32 gradients; every gradient at head dim 256)."""
     if bias.dtype == q.dtype:
-        return _empty_dbias(bias, q.dtype)
+        return _empty_dbias(bias, q.dtype, zero=bool(causal) and q.shape[-1] == 256)
     return _empty_dbias(bias, torch.float32, zero=bool(causal))
 
 
