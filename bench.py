@@ -58,12 +58,15 @@ WORKLOADS = {
     "3": dict(B=8, H=16, M=2048, N=2048, D=128, dtype="bf16", bias="float", causal=False, bias_scale=0.5, passes=24),
     "4": dict(B=4, H=32, M=4096, N=4096, D=128, dtype="bf16", bias="bool", causal=True, bias_scale=0.0, passes=12),
     "5": dict(B=8, H=32, M=8192, N=8192, D=128, dtype="bf16", bias="float", causal=True, bias_scale=0.5, passes=2),
+    # not a benchmark configuration of the reference: the largest head dim its API accepts
+    "d256": dict(B=4, H=8, M=2048, N=2048, D=256, dtype="bf16", bias="float", causal=False, bias_scale=0.5, passes=12),
 }
 WORKLOAD_NAMES = {
     "2": "config2: causal self-attention B4 H16 M=N=1024 D64 bf16, no bias",
     "3": "config3: B8 H16 M=N=2048 D128 bf16, trainable float bias (B,H,M,N), non-causal",
     "4": "config4: bool mask + causal B4 H32 S4096 D128 bf16",
     "5": "config5: B8 H32 M=N=8192 D128 bf16, trainable float bias, causal",
+    "d256": "head dim 256: B4 H8 M=N=2048 D256 bf16, trainable float bias, non-causal",
 }
 # ncu summary of one dK/dV launch of the default workload at a reduced batch (traffic is
 # proportional to the batch); parsed for dram__bytes_{read,write}.sum

@@ -62,7 +62,6 @@ struct FwdParams {
   int o_vec32;  // o's base and strides are multiples of 32 bytes
   int bias_b_mul, bias_h_mul;
   int n_mblk, n_pairs, n_units;  // query blocks / block pairs per (batch, head); units = pairs * B * H
-  int tiles;                     // query tiles per unit: 2, or 1 at head dim 256
   float sm_scale;
 };
 
@@ -98,6 +97,7 @@ struct Unit {
   int nmax;
   __device__ __forceinline__ int nb(int t) const { return t ? nb1 : nb0; }
 };
+template <int TILES>  // query tiles per unit: 2, or 1 at head dim 256
 __device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
   const int sh = p.causal ? 1 : 0;
   const int c = static_cast<int>(blockIdx.x) + (it >> sh) * static_cast<int>(gridDim.x);
@@ -106,10 +106,10 @@ __device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
   u.bh = k / p.n_pairs;
   const int pos = k - u.bh * p.n_pairs;
   const int pair = p.causal ? ((pos & 1) ? (pos >> 1) : p.n_pairs - 1 - (pos >> 1)) : pos;
-  u.mb0 = pair * p.tiles;
+  u.mb0 = pair * TILES;
   const int nblk_all = (p.N + 127) >> 7;
   u.nb0 = u.mb0 >= p.n_mblk ? 0 : (p.causal ? min(nblk_all, u.mb0 + 1) : nblk_all);
-  u.nb1 = (p.tiles < 2 || u.mb0 + 1 >= p.n_mblk) ? 0 : (p.causal ? min(nblk_all, u.mb0 + 2) : nblk_all);
+  u.nb1 = (TILES < 2 || u.mb0 + 1 >= p.n_mblk) ? 0 : (p.causal ? min(nblk_all, u.mb0 + 2) : nblk_all);
   u.nmax = max(u.nb0, u.nb1);
   return true;
 }
@@ -117,7 +117,7 @@ __device__ __forceinline__ bool unit_at(const FwdParams& p, int it, Unit& u) {
 // Walks the bias units of this CTA in the order the softmax groups consume them:
 // per unit, per key block j, per tile t (if it visits j): two 64-key halves (16-bit bias),
 // four 32-key quarters (fp32 bias) or one unit (byte mask, [128][128] bytes per block).
-template <int BIAS>
+template <int BIAS, int TILES>
 struct BiasWalk {
   static constexpr int kSub = BIAS == 1 ? 2 : (BIAS == 3 ? 4 : 1);  // units per (tile, block)
   int it = 0, j = 0, t = 0, h = 0;
@@ -130,7 +130,7 @@ struct BiasWalk {
         ++it;
         j = 0;
         t = 0;
-        valid = unit_at(p, it, u);
+        valid = unit_at<TILES>(p, it, u);
         continue;
       }
       if (t >= 2) {
@@ -146,7 +146,7 @@ struct BiasWalk {
     }
   }
   __device__ __forceinline__ void start(const FwdParams& p) {
-    valid = unit_at(p, 0, u);
+    valid = unit_at<TILES>(p, 0, u);
     settle(p);
   }
   __device__ __forceinline__ void next(const FwdParams& p) {
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
       bool ok = true;
       uint32_t gk = 0, gv = 0;  // key blocks / V halves issued so far, over all units
       Unit u;
-      for (int it = 0; ok && unit_at(p, it, u); ++it) {
+      for (int it = 0; ok && unit_at<L::kTiles>(p, it, u); ++it) {
         const int b = u.bh / p.H, h = u.bh - b * p.H;
         // the Q pair is free once every Q K^T product of the previous unit is through
         if (it >= 1) ok = mbar_wait(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
                                            kBlk, kBlk, idesc_qk, false);
         mma_commit(&s_full[t][keys]);
       };
-      for (int it = 0; ok && unit_at(p, it, u); ++it) {
+      for (int it = 0; ok && unit_at<L::kTiles>(p, it, u); ++it) {
         if (u.nmax == 0) continue;
         const int nblk = u.nb(t);
         ok = mbar_wait(&q_full, it & 1, ctx, kSiteQFull, it);
@@ -363,10 +363,10 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
     if (BIAS != 0 && lane == 0 && live) {
       tma_prefetch_desc(&p.map_bias);
       const uint64_t pol_stream = policy_evict_first();
-      BiasWalk<BIAS> cur, ahead;
+      BiasWalk<BIAS, L::kTiles> cur, ahead;
       cur.start(p);
       ahead.start(p);
-      auto l2 = [&](const BiasWalk<BIAS>& wk) {
+      auto l2 = [&](const BiasWalk<BIAS, L::kTiles>& wk) {
         int n0, m0, hh, bb;
         wk.coords(p, n0, m0, hh, bb);
         if (n0 < p.N) tma_prefetch_l2_4d(&p.map_bias, n0, m0, hh, bb);
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
     // b_phase is the parity of this group's next unit in slot s.
     uint32_t b_phase = 0;
     Unit u;
-    for (int it = 0; ok && unit_at(p, it, u); ++it) {
+    for (int it = 0; ok && unit_at<L::kTiles>(p, it, u); ++it) {
       const int nblk = u.nb(t);
       const int m0 = (u.mb0 + t) * 128;
       float m_used = -INFINITY;  // running maximum, log2 domain
@@ -727,8 +727,8 @@ int launch_fwd(const fa_params& p, cudaStream_t stream, int* status) {
   fp.sm_scale = p.sm_scale;
   fp.n_mblk = (p.M + 127) / 128;
   const int dp = padded_head_dim(p.D);
-  fp.tiles = dp == 256 ? 1 : 2;
-  fp.n_pairs = (fp.n_mblk + fp.tiles - 1) / fp.tiles;
+  const int tiles = dp == 256 ? 1 : 2;  // query tiles per unit (FwdSmem::kTiles)
+  fp.n_pairs = (fp.n_mblk + tiles - 1) / tiles;
   fp.n_units = fp.n_pairs * p.B * p.H;
   const dim3 grid(persistent_grid(p.causal ? (fp.n_units + 1) / 2 : fp.n_units));
   if (p.dtype == FA_BF16) {
