@@ -111,7 +111,9 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // the warp index as a value the compiler knows to be the same in all lanes: the role
+  // branches below are then warp-uniform and the issuer warps run converged
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   const int n_mblk = (p.M + 127) >> 7;
 
@@ -244,7 +246,10 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     }
   } else if (warp == 17) {
     // ------------------------------------------------------- MMA issuer: S and dP
-    if (lane == 0 && live) {
+    // The whole warp walks the loop (waits included) and one elected lane issues: the
+    // descriptors are then warp-uniform values, which the tensor-core instructions take
+    // without a per-operand transfer from a lane's registers.
+    if (live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
       const uint32_t k_addr = smem_u32(smem + L::kK), v_addr = smem_u32(smem + L::kV);
@@ -258,34 +263,38 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       int bh, nb, i_start, T_steps;
       for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
         if (T_steps <= 0) continue;
-        ok = mbar_wait(&kv_full, kvi & 1, ctx, kSiteKV, it);
+        ok = wait_warp(&kv_full, kvi & 1, ctx, kSiteKV, it);
         ++kvi;
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
           const int qs = gs & 1, ds = gs % kDoStages;
           const uint32_t q_par = (gs >> 1) & 1, do_par = (gs / kDoStages) & 1;
           // S_gs: its columns are free once the row threads hold S_{gs-1} in registers
-          const uint32_t pq = mbar_poll(&q_full[qs], q_par);
-          if (gs >= 1) ok = mbar_wait_hot(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
-          if (ok) ok = wait_polled(pq, &q_full[qs], q_par, ctx, kSiteQFull, t);
+          if (gs >= 1) ok = wait_warp_hot(&s_free, (gs - 1) & 1, ctx, kSiteSFree, t);
+          if (ok) ok = wait_warp(&q_full[qs], q_par, ctx, kSiteQFull, t);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t pdo = mbar_poll(&do_full[ds], do_par);
-          issue_gemm_ss<KS_D, false, false>(tmem + kColS, qs ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
-                                            idesc_s, false);
-          mma_commit(&s_full);
-          mma_commit(&q_empty[qs]);
+          if (elect_one()) {
+            issue_gemm_ss<KS_D, false, false>(tmem + kColS, qs ? q_km_1 : q_km_0, k_km, kBlk, kBlk,
+                                              idesc_s, false);
+            mma_commit(&s_full);
+            mma_commit(&q_empty[qs]);
+          }
+          __syncwarp();
           // dP_gs: same for the dP columns; dO_gs replaces dO_{gs-1} after dV_{gs-1} when
           // single-staged
-          if (gs >= 1) ok = mbar_wait_hot(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
-          if (ok) ok = wait_polled(pdo, &do_full[ds], do_par, ctx, kSiteDoFull, t);
+          if (gs >= 1) ok = wait_warp_hot(&dp_free, (gs - 1) & 1, ctx, kSiteDpFree, t);
+          if (ok) ok = wait_warp(&do_full[ds], do_par, ctx, kSiteDoFull, t);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ds ? do_km_1 : do_km_0, v_km, kBlk, kBlk,
-                                            idesc_s, false);
-          mma_commit(&dp_full);
-          mma_commit(&do_empty[ds]);
-          if (t == T_steps - 1) mma_commit(&kv_empty);  // K and V may be replaced
+          if (elect_one()) {
+            issue_gemm_ss<KS_D, false, false>(tmem + kColDp, ds ? do_km_1 : do_km_0, v_km, kBlk, kBlk,
+                                              idesc_s, false);
+            mma_commit(&dp_full);
+            mma_commit(&do_empty[ds]);
+            if (t == T_steps - 1) mma_commit(&kv_empty);  // K and V may be replaced
+          }
+          __syncwarp();
         }
         g += T_steps;
       }
@@ -293,7 +302,8 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     __syncwarp();
   } else if (warp == 18) {
     // ------------------------------------------------------ MMA issuer: dV and dK
-    if (lane == 0 && live) {
+    // (whole warp converged, one elected lane issues: see the S / dP issuer)
+    if (live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_g = make_idesc(bf, true, true, 128, DP);
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
@@ -302,13 +312,13 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       const uint64_t do_mn_0 = make_sdesc(do_addr, kBlk, 1024),
                      do_mn_1 = make_sdesc(do_addr + (kDoStages - 1) * L::kTile, kBlk, 1024);
       const uint64_t p_mn = make_sdesc(p_addr, kBlk, 1024), ds_mn = make_sdesc(ds_addr, kBlk, 1024);
-      // This thread also sends the dS tiles out as dbias (a bias gradient only exists for a
+      // The elected lane also sends the dS tiles out as dbias (a bias gradient only exists for a
       // 16-bit bias).  st_done completes once per step when the store of dS has finished
       // reading sDS and - causal only - once per tile before that, when the zero tiles above
       // the diagonal are out.  (Without the zero tiles there is no per-tile completion: two
       // completions in a row that no row thread has to wait for in between would let a parity
       // wait fall two phases behind.)  The wait for the store's read sits right after the
-      // store: the next thing this thread needs, P of the next step, is further away.
+      // store: the next thing this warp needs, P of the next step, is further away.
       const bool stores_here = p.store_ds != 0;
       bool zeros_in_flight = false;
       bool ok = true;
@@ -317,22 +327,24 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
       for (int it = 0; ok && tile_at(it, bh, nb, i_start, T_steps); ++it) {
         const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
         if (p.zero_tiles) {
-          ok = mbar_wait(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
+          ok = wait_warp(&zero_ready, it & 1, ctx, kSiteZeroReady, it);
           if (!ok) break;
-          for (int i = 0; i < i_start; ++i) {
-            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
-            if (n0 + 64 < p.N)
-              tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
+          if (elect_one()) {
+            for (int i = 0; i < i_start; ++i) {
+              tma_store_4d(&p.map_dbias, smem + L::kDs, n0, i * 128, h, b);
+              if (n0 + 64 < p.N)
+                tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, i * 128, h, b);
+            }
+            tma_store_commit();
+            if (T_steps <= 0) {
+              tma_store_wait_read<0>();
+              mbar_arrive(&st_done);
+            }
           }
-          tma_store_commit();
+          __syncwarp();
           // the zero tiles are read out of sDS while P of the first step is formed and dV is
-          // issued; their completion is announced just before this thread needs dS
-          zeros_in_flight = true;
-          if (T_steps <= 0) {
-            tma_store_wait_read<0>();
-            mbar_arrive(&st_done);
-            zeros_in_flight = false;
-          }
+          // issued; their completion is announced just before this warp needs dS
+          zeros_in_flight = T_steps > 0;
         }
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
@@ -341,42 +353,46 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           // dV += P^T dO  (dO must have landed: P only depends on S).  The first product of a
           // tile overwrites dV / dK: P and dS of a new tile are only announced by all sixteen
           // row warps after they have read the previous tile's accumulators.
-          const uint32_t pdo = mbar_poll(&do_full[ds], (gs / kDoStages) & 1);
-          const uint32_t pq = mbar_poll(&q_full[qs], (gs >> 1) & 1);
-          ok = mbar_wait_hot(&p_ready, gs & 1, ctx, kSitePReady, t);
-          if (ok) ok = wait_polled(pdo, &do_full[ds], (gs / kDoStages) & 1, ctx, kSiteDoFull, t);
+          ok = wait_warp_hot(&p_ready, gs & 1, ctx, kSitePReady, t);
+          if (ok) ok = wait_warp(&do_full[ds], (gs / kDoStages) & 1, ctx, kSiteDoFull, t);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
-                                       t > 0);
-          mma_commit(&do_empty[ds]);
-          mma_commit(&dv_done);
-          if (zeros_in_flight) {
-            tma_store_wait_read<0>();
-            mbar_arrive(&st_done);
-            zeros_in_flight = false;
+          if (elect_one()) {
+            issue_gemm_ss<8, true, true>(tmem + kColDv, p_mn, ds ? do_mn_1 : do_mn_0, kBlk, kBlk, idesc_g,
+                                         t > 0);
+            mma_commit(&do_empty[ds]);
+            mma_commit(&dv_done);
+            if (zeros_in_flight) {
+              tma_store_wait_read<0>();
+              mbar_arrive(&st_done);
+            }
           }
+          __syncwarp();
+          zeros_in_flight = false;
           // dK += dS^T Q
-          ok = mbar_wait_hot(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
-          if (ok) ok = wait_polled(pq, &q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
+          ok = wait_warp_hot(&ds_ready, gs & 1, ctx, kSiteDsReady, t);
+          if (ok) ok = wait_warp(&q_full[qs], (gs >> 1) & 1, ctx, kSiteQFull, t);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
-                                       t > 0);
-          mma_commit(&q_empty[qs]);
-          mma_commit(&dk_done);
-          if (stores_here) {
-            const int m0 = (i_start + t) * 128;
-            tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
-            if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
-            tma_store_commit();
-            tma_store_wait_read<0>();
-            mbar_arrive(&st_done);
+          if (elect_one()) {
+            issue_gemm_ss<8, true, true>(tmem + kColDk, ds_mn, qs ? q_mn_1 : q_mn_0, kBlk, kBlk, idesc_g,
+                                         t > 0);
+            mma_commit(&q_empty[qs]);
+            mma_commit(&dk_done);
+            if (stores_here) {
+              const int m0 = (i_start + t) * 128;
+              tma_store_4d(&p.map_dbias, smem + L::kDs, n0, m0, h, b);
+              if (n0 + 64 < p.N) tma_store_4d(&p.map_dbias, smem + L::kDs + kBlk, n0 + 64, m0, h, b);
+              tma_store_commit();
+              tma_store_wait_read<0>();
+              mbar_arrive(&st_done);
+            }
           }
+          __syncwarp();
         }
         g += T_steps;
       }
-      if (stores_here) tma_store_wait_all<0>();
+      if (stores_here && elect_one()) tma_store_wait_all<0>();
     }
     __syncwarp();
   } else if (warp == 19) {

@@ -82,7 +82,9 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // the warp index as a value the compiler knows to be the same in all lanes: the issuer
+  // warps then run converged and only elect a lane for the issue itself
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
 
   // Persistent CTA with the schedule of the forward kernel: tiles (128 query rows of one
@@ -177,7 +179,8 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
     }
   } else if (warp == 17) {
     // ------------------------------------------------------- MMA issuer: S and dP
-    if (lane == 0 && live) {
+    // (whole warp converged, one elected lane issues: the descriptors stay warp-uniform)
+    if (live) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 128);
       const uint32_t q_addr = smem_u32(smem + L::kQ), do_addr = smem_u32(smem + L::kDo);
@@ -193,27 +196,31 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
           const uint32_t g = gj + j;
           const int st = g & 1;
           const uint32_t ph = (g >> 1) & 1;
-          const uint32_t pk = mbar_poll(&k_full[st], ph);
-          const uint32_t pv = mbar_poll(&v_full[st], ph);
           // S_g: its columns are free once the row threads hold S_{g-1} in registers
-          if (g >= 1) ok = mbar_wait_hot(&s_free, (g - 1) & 1, ctx, kSiteSFree, j);
-          if (ok && j == 0) ok = mbar_wait(&qdo_full, it & 1, ctx, kSiteQdo, it);
-          if (ok) ok = wait_polled(pk, &k_full[st], ph, ctx, kSiteKFull, j);
+          if (g >= 1) ok = wait_warp_hot(&s_free, (g - 1) & 1, ctx, kSiteSFree, j);
+          if (ok && j == 0) ok = wait_warp(&qdo_full, it & 1, ctx, kSiteQdo, it);
+          if (ok) ok = wait_warp(&k_full[st], ph, ctx, kSiteKFull, j);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, st ? k_km_1 : k_km_0, kBlk, kBlk,
-                                            idesc_s, false);
-          mma_commit(&s_full);
-          mma_commit(&k_empty[st]);
-          if (g >= 1) ok = mbar_wait_hot(&dp_free, (g - 1) & 1, ctx, kSiteDpFree, j);
-          if (ok) ok = wait_polled(pv, &v_full[st], ph, ctx, kSiteVFull, j);
+          if (elect_one()) {
+            issue_gemm_ss<KS_D, false, false>(tmem + kColS, q_km, st ? k_km_1 : k_km_0, kBlk, kBlk,
+                                              idesc_s, false);
+            mma_commit(&s_full);
+            mma_commit(&k_empty[st]);
+          }
+          __syncwarp();
+          if (g >= 1) ok = wait_warp_hot(&dp_free, (g - 1) & 1, ctx, kSiteDpFree, j);
+          if (ok) ok = wait_warp(&v_full[st], ph, ctx, kSiteVFull, j);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, st ? v_km_1 : v_km_0, kBlk, kBlk,
-                                            idesc_s, false);
-          mma_commit(&dp_full);
-          mma_commit(&v_empty[st]);
-          if (j == nblk - 1) mma_commit(&qdo_empty);  // Q and dO may be replaced
+          if (elect_one()) {
+            issue_gemm_ss<KS_D, false, false>(tmem + kColDp, do_km, st ? v_km_1 : v_km_0, kBlk, kBlk,
+                                              idesc_s, false);
+            mma_commit(&dp_full);
+            mma_commit(&v_empty[st]);
+            if (j == nblk - 1) mma_commit(&qdo_empty);  // Q and dO may be replaced
+          }
+          __syncwarp();
         }
         gj += nblk;
       }
@@ -221,7 +228,7 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
     __syncwarp();
   } else if (warp == 18) {
     // ------------------------------------------------------- MMA issuer: dQ += dS K
-    if (lane == 0 && live) {
+    if (live) {
       constexpr uint32_t idesc_dq = make_idesc(P2::kIsBf16, false, true, 128, DP);
       const uint32_t k_addr = smem_u32(smem + L::kK);
       const uint64_t k_mn_0 = make_sdesc(k_addr, kBlk, 1024), k_mn_1 = make_sdesc(k_addr + L::kTile, kBlk, 1024);
@@ -233,17 +240,19 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
         for (int j = 0; j < nblk && ok; ++j) {
           const uint32_t g = gj + j;
           const int st = g & 1;
-          const uint32_t pk = mbar_poll(&k_full[st], (g >> 1) & 1);
           // dS of a new tile is only announced by all sixteen row warps after they have read
           // the previous tile's dQ, so the first product of a tile may overwrite it
-          ok = mbar_wait_hot(&ds_ready, g & 1, ctx, kSiteDsReady, j);
-          if (ok) ok = wait_polled(pk, &k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
+          ok = wait_warp_hot(&ds_ready, g & 1, ctx, kSiteDsReady, j);
+          if (ok) ok = wait_warp(&k_full[st], (g >> 1) & 1, ctx, kSiteKFull, j);
           if (!ok) break;
           tc_fence_after();
-          issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, st ? k_mn_1 : k_mn_0, kBlk, kBlk, idesc_dq,
-                                        j > 0);
-          mma_commit(&k_empty[st]);
-          mma_commit(&dq_done);
+          if (elect_one()) {
+            issue_gemm_ss<8, false, true>(tmem + kColDq, ds_km, st ? k_mn_1 : k_mn_0, kBlk, kBlk, idesc_dq,
+                                          j > 0);
+            mma_commit(&k_empty[st]);
+            mma_commit(&dq_done);
+          }
+          __syncwarp();
         }
         gj += nblk;
       }
@@ -413,7 +422,9 @@ __global__ void __launch_bounds__(192, 2) dq_from_ds_kernel(const __grid_constan
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // the warp index as a value the compiler knows to be the same in all lanes: the issuer
+  // warps then run converged and only elect a lane for the issue itself
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   const int m_block = gridDim.x - 1 - blockIdx.x;
   // the (batch, head) problems in reverse: the dS tiles written last by the dK/dV kernel are
@@ -469,21 +480,25 @@ __global__ void __launch_bounds__(192, 2) dq_from_ds_kernel(const __grid_constan
       }
     }
   } else if (warp == 5) {
-    if (lane == 0 && live) {
+    // (whole warp converged, one elected lane issues)
+    if (live) {
       constexpr uint32_t idesc = make_idesc(P2::kIsBf16, false, true, 128, DP);
       bool ok = true;
       for (int s = 0; s < nsteps && ok; ++s) {
         const int st = s % L::kStages;
-        ok = mbar_wait(&full[st], (s / L::kStages) & 1, ctx, kSiteStageFull, s);
+        ok = wait_warp(&full[st], (s / L::kStages) & 1, ctx, kSiteStageFull, s);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + st * L::kStage);
         const uint32_t b_addr = a_addr + L::kDsBytes;
-        issue_gemm_ss<4, false, true>(tmem, make_sdesc(a_addr, 0, 1024),
-                                      make_sdesc(b_addr, 64 * 128, 1024), 0, 0, idesc, s > 0);
-        mma_commit(&empty[st]);
+        if (elect_one()) {
+          issue_gemm_ss<4, false, true>(tmem, make_sdesc(a_addr, 0, 1024),
+                                        make_sdesc(b_addr, 64 * 128, 1024), 0, 0, idesc, s > 0);
+          mma_commit(&empty[st]);
+        }
+        __syncwarp();
       }
-      if (ok) mma_commit(&acc_done);
+      if (ok && elect_one()) mma_commit(&acc_done);
     }
     __syncwarp();
   } else {

@@ -654,6 +654,14 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, const 
   return __all_sync(0xffffffffu, ok);
 }
 
+// The same for a converged control warp on the critical path: every lane polls without
+// suspending first.
+__device__ __forceinline__ bool wait_warp_hot(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+                                              int site, int iter) {
+  const bool ok = mbar_wait_hot(bar, parity, ctx, site, iter);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Finish a wait whose phase was polled earlier: no further barrier traffic when the
 // poll had already seen the phase complete.
 __device__ __forceinline__ bool wait_polled(uint32_t polled, uint64_t* bar, uint32_t parity,

@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // the warp index as a value the compiler knows to be the same in all lanes
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
 
   WaitCtx ctx{&abort_flag, p.status, 1};
@@ -274,7 +275,8 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
     }
   } else if (warp == 9 || warp == 11) {
     // ------------------------------------------- MMA issuer of tile slot t (one lane)
-    if (lane == 0 && live) {
+    // (the whole warp walks the loop converged, one elected lane issues)
+    if (live) {
       const int t = warp == 9 ? 0 : 1;
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_qk = make_idesc(bf, false, false, 128, 64);
@@ -288,24 +290,31 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
       Unit u;
       // scores of one 64-key half of the block in ring stage `kslot` -> column half `ch`
       auto issue_qk = [&](uint32_t kslot, int keys, uint32_t ch) {
-        issue_gemm_ss<KS_QK, false, false>(tm_s + ch * 64, make_sdesc(q_addr, 0, 1024),
-                                           make_sdesc(k_addr + kslot * L::kKStage + keys * (64 * 128), 0, 1024),
-                                           kBlk, kBlk, idesc_qk, false);
-        mma_commit(&s_full[t][keys]);
+        if (elect_one()) {
+          issue_gemm_ss<KS_QK, false, false>(tm_s + ch * 64, make_sdesc(q_addr, 0, 1024),
+                                             make_sdesc(k_addr + kslot * L::kKStage + keys * (64 * 128), 0, 1024),
+                                             kBlk, kBlk, idesc_qk, false);
+          mma_commit(&s_full[t][keys]);
+        }
+        __syncwarp();
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (elect_one()) mma_commit(bar);
+        __syncwarp();
       };
       for (int it = 0; ok && unit_at<L::kTiles>(p, it, u); ++it) {
         if (u.nmax == 0) continue;
         const int nblk = u.nb(t);
-        ok = mbar_wait(&q_full, it & 1, ctx, kSiteQFull, it);
-        if (ok) ok = mbar_wait(&k_full[gk % KST], (gk / KST) & 1, ctx, kSiteKFull, 0);
+        ok = wait_warp(&q_full, it & 1, ctx, kSiteQFull, it);
+        if (ok) ok = wait_warp(&k_full[gk % KST], (gk / KST) & 1, ctx, kSiteKFull, 0);
         if (!ok) break;
         tc_fence_after();
         if (nblk > 0) {
           issue_qk(gk % KST, 0, cs & 1);
           issue_qk(gk % KST, 1, (cs & 1) ^ 1);
         }
-        mma_commit(&k_empty[gk % KST]);
-        if (u.nmax == 1) mma_commit(&q_empty);
+        commit(&k_empty[gk % KST]);
+        if (u.nmax == 1) commit(&q_empty);
         for (int j = 0; j < u.nmax && ok; ++j) {
           const uint32_t kn = (gk + j + 1) % KST, kn_par = ((gk + j + 1) / KST) & 1;
           const bool more = j + 1 < u.nmax;  // the unit has a block j+1 (this tile may not visit it)
@@ -315,27 +324,29 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
             const uint32_t gh = gv + 2 * j + h;
             const uint32_t vs = gh % VS, v_par = (gh / VS) & 1;
             if (mine) {
-              const uint32_t pv = mbar_poll(&v_full[vs], v_par);
-              ok = mbar_wait_hot(&p_full[t][h], cs & 1, ctx, kSitePFull, j);
-              if (ok) ok = wait_polled(pv, &v_full[vs], v_par, ctx, kSiteVFull, j);
+              ok = wait_warp_hot(&p_full[t][h], cs & 1, ctx, kSitePFull, j);
+              if (ok) ok = wait_warp(&v_full[vs], v_par, ctx, kSiteVFull, j);
               if (!ok) break;
               tc_fence_after();
-              issue_gemm_ts<4, true>(tm_o, tm_s + f * 64 + h * 32,
-                                     make_sdesc(v_addr + vs * L::kVHalf, kVBlk, 1024), kVBlk, idesc_pv,
-                                     j > 0 || h > 0);
-              mma_commit(&pv_done[t][h]);
+              if (elect_one()) {
+                issue_gemm_ts<4, true>(tm_o, tm_s + f * 64 + h * 32,
+                                       make_sdesc(v_addr + vs * L::kVHalf, kVBlk, 1024), kVBlk, idesc_pv,
+                                       j > 0 || h > 0);
+                mma_commit(&pv_done[t][h]);
+              }
+              __syncwarp();
             } else {
               // a block only the other tile visits: keep the ring counters in step
-              ok = mbar_wait(&v_full[vs], v_par, ctx, kSiteVFull, j);
+              ok = wait_warp(&v_full[vs], v_par, ctx, kSiteVFull, j);
               if (!ok) break;
             }
-            mma_commit(&v_empty[vs]);
+            commit(&v_empty[vs]);
             if (h == 0) {
               // Keys 0-63 of block j+1 go into the column half whose scores (keys 64-127 of
               // block j) the row threads have just taken into registers: this product runs
               // under the second half of this step's softmax.
-              if (mine) ok = mbar_wait_hot(&s_read[t], cs & 1, ctx, kSiteSRead, j);
-              if (ok && more) ok = mbar_wait(&k_full[kn], kn_par, ctx, kSiteKFull, j + 1);
+              if (mine) ok = wait_warp_hot(&s_read[t], cs & 1, ctx, kSiteSRead, j);
+              if (ok && more) ok = wait_warp(&k_full[kn], kn_par, ctx, kSiteKFull, j + 1);
               if (!ok) break;
               if (mine_next) {
                 tc_fence_after();
@@ -346,8 +357,8 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
               // issuing thread, so it executes after the products just issued.
               if (mine_next) issue_qk(kn, 1, f);
               if (more) {
-                mma_commit(&k_empty[kn]);
-                if (j + 2 >= u.nmax) mma_commit(&q_empty);
+                commit(&k_empty[kn]);
+                if (j + 2 >= u.nmax) commit(&q_empty);
               }
             }
           }
