@@ -401,8 +401,9 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
     // will then write P (same two swizzled blocks, every thread reads the four 16-byte
     // chunks it is about to overwrite): no extra shared memory.  sP is free for it once the
     // dV product of the previous step has read P.
-    if (BIAS == 1 && lane == 0 && live) {
-      tma_prefetch_desc(&p.map_bias);
+    // (whole warp converged, one elected lane issues: the load follows the barrier sooner)
+    if (BIAS == 1 && live) {
+      if (lane == 0) tma_prefetch_desc(&p.map_bias);
       bool ok = true;
       uint32_t g = 0;
       int bh, nb, i_start, T_steps;
@@ -411,15 +412,18 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         const bool two = n0 + 64 < p.N;
         for (int t = 0; t < T_steps && ok; ++t) {
           const uint32_t gs = g + t;
-          if (gs >= 1) ok = mbar_wait_hot(&dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
+          if (gs >= 1) ok = wait_warp_hot(&dv_done, (gs - 1) & 1, ctx, kSiteDvDone, t);
           if (!ok) break;
           const int m0 = (i_start + t) * 128;
-          mbar_expect_tx(&bias_full, two ? 2 * kBlk : kBlk);
-          tma_load_4d(smem + L::kP, &p.map_bias, &bias_full, n0, m0, h * p.bias_h_mul,
-                      b * p.bias_b_mul);
-          if (two)
-            tma_load_4d(smem + L::kP + kBlk, &p.map_bias, &bias_full, n0 + 64, m0, h * p.bias_h_mul,
+          if (elect_one()) {
+            mbar_expect_tx(&bias_full, two ? 2 * kBlk : kBlk);
+            tma_load_4d(smem + L::kP, &p.map_bias, &bias_full, n0, m0, h * p.bias_h_mul,
                         b * p.bias_b_mul);
+            if (two)
+              tma_load_4d(smem + L::kP + kBlk, &p.map_bias, &bias_full, n0 + 64, m0, h * p.bias_h_mul,
+                          b * p.bias_b_mul);
+          }
+          __syncwarp();
         }
         g += T_steps;
       }

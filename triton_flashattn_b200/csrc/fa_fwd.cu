@@ -235,40 +235,52 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
 
   if (warp == 8) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && live) {
-      tma_prefetch_desc(&p.map_q);
-      tma_prefetch_desc(&p.map_k);
-      tma_prefetch_desc(&p.map_v);
+    // (whole warp converged, one elected lane issues)
+    if (live) {
+      if (lane == 0) {
+        tma_prefetch_desc(&p.map_q);
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
+      }
       bool ok = true;
       uint32_t gk = 0, gv = 0;  // key blocks / V halves issued so far, over all units
       Unit u;
       for (int it = 0; ok && unit_at<L::kTiles>(p, it, u); ++it) {
         const int b = u.bh / p.H, h = u.bh - b * p.H;
         // the Q pair is free once every Q K^T product of the previous unit is through
-        if (it >= 1) ok = mbar_wait(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
+        if (it >= 1) ok = wait_warp(&q_empty, (it - 1) & 1, ctx, kSiteQEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&q_full, L::kTiles * L::kQTile);
-        for (int t = 0; t < L::kTiles; ++t)
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kQ + t * L::kQTile + kb * kBlk, &p.map_q, &q_full, kb * 64, h,
-                        (u.mb0 + t) * 128, b);
+        if (elect_one()) {
+          mbar_expect_tx(&q_full, L::kTiles * L::kQTile);
+          for (int t = 0; t < L::kTiles; ++t)
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kQ + t * L::kQTile + kb * kBlk, &p.map_q, &q_full, kb * 64, h,
+                          (u.mb0 + t) * 128, b);
+        }
+        __syncwarp();
         for (int j = 0; j < u.nmax && ok; ++j, ++gk) {
           const uint32_t ks = gk % KST;
           const int n0 = j * 128;
-          if (gk >= KST) ok = mbar_wait(&k_empty[ks], (gk / KST - 1) & 1, ctx, kSiteKEmpty, j);
+          if (gk >= KST) ok = wait_warp(&k_empty[ks], (gk / KST - 1) & 1, ctx, kSiteKEmpty, j);
           if (!ok) break;
-          mbar_expect_tx(&k_full[ks], L::kKStage);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kK + ks * L::kKStage + kb * kBlk, &p.map_k, &k_full[ks], kb * 64, h,
-                        n0, b);
+          if (elect_one()) {
+            mbar_expect_tx(&k_full[ks], L::kKStage);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kK + ks * L::kKStage + kb * kBlk, &p.map_k, &k_full[ks], kb * 64, h,
+                          n0, b);
+          }
+          __syncwarp();
           for (int hf = 0; hf < 2 && ok; ++hf, ++gv) {
             const uint32_t vs = gv % VS, use = gv / VS;
-            if (use >= 1) ok = mbar_wait(&v_empty[vs], (use - 1) & 1, ctx, kSiteVEmpty, j);
+            if (use >= 1) ok = wait_warp(&v_empty[vs], (use - 1) & 1, ctx, kSiteVEmpty, j);
             if (!ok) break;
-            mbar_expect_tx(&v_full[vs], L::kVHalf);
-            for (int kb = 0; kb < KB; ++kb)
-              tma_load_4d(smem + L::kV + vs * L::kVHalf + kb * kVBlk, &p.map_v, &v_full[vs], kb * 64, h,
-                          n0 + hf * 64, b);
+            if (elect_one()) {
+              mbar_expect_tx(&v_full[vs], L::kVHalf);
+              for (int kb = 0; kb < KB; ++kb)
+                tma_load_4d(smem + L::kV + vs * L::kVHalf + kb * kVBlk, &p.map_v, &v_full[vs], kb * 64, h,
+                            n0 + hf * 64, b);
+            }
+            __syncwarp();
           }
         }
       }
@@ -371,8 +383,9 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
     __syncwarp();
   } else if (warp == 10) {
     // ------------------------------------------------------------ bias producer
-    if (BIAS != 0 && lane == 0 && live) {
-      tma_prefetch_desc(&p.map_bias);
+    // (whole warp converged, one elected lane issues)
+    if (BIAS != 0 && live) {
+      if (lane == 0) tma_prefetch_desc(&p.map_bias);
       const uint64_t pol_stream = policy_evict_first();
       BiasWalk<BIAS, L::kTiles> cur, ahead;
       cur.start(p);
@@ -380,7 +393,8 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
       auto l2 = [&](const BiasWalk<BIAS, L::kTiles>& wk) {
         int n0, m0, hh, bb;
         wk.coords(p, n0, m0, hh, bb);
-        if (n0 < p.N) tma_prefetch_l2_4d(&p.map_bias, n0, m0, hh, bb);
+        if (n0 < p.N && elect_one()) tma_prefetch_l2_4d(&p.map_bias, n0, m0, hh, bb);
+        __syncwarp();
       };
       for (int i = 0; i < kPf && ahead.valid; ++i) {
         l2(ahead);
@@ -393,14 +407,17 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
           ahead.next(p);
         }
         const uint32_t bs = unit % NB, use = unit / NB;
-        if (use >= 1) ok = mbar_wait(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, cur.j);
+        if (use >= 1) ok = wait_warp(&bias_empty[bs], (use - 1) & 1, ctx, kSiteBiasEmpty, cur.j);
         if (!ok) break;
         int n0, m0, hh, bb;
         cur.coords(p, n0, m0, hh, bb);
         // the "full" barrier of the group that will read this unit (see the softmax side)
         uint64_t* full = &bias_full[cur.t][bs];
-        mbar_expect_tx(full, kBlk);
-        tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, full, n0, m0, hh, bb, pol_stream);
+        if (elect_one()) {
+          mbar_expect_tx(full, kBlk);
+          tma_load_4d_hint(smem + L::kBias + bs * kBlk, &p.map_bias, full, n0, m0, hh, bb, pol_stream);
+        }
+        __syncwarp();
         cur.next(p);
       }
     }
