@@ -8,11 +8,11 @@
 // epilogue.  Roles (640 threads):
 //   warps 0-15 "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
 //              (query rows of the block) and on the 32-key column quarter (w>>2)
-//   warp 16    TMA producer (one lane): K, V per tile; Q ring (2), dO ring; bias tiles
+//   warp 16    TMA producer (converged, an elected lane issues): K, V per tile; Q ring (2), dO ring; bias tiles
 //              are asked into L2 two steps ahead
-//   warp 17    MMA issuer for S and dP (one lane), tensor-memory owner
-//   warp 18    MMA issuer for dV and dK, bulk tensor stores of dS into dbias (one lane)
-//   warp 19    TMA loads of the 16-bit bias tiles (one lane)
+//   warp 17    MMA issuer for S and dP (converged, an elected lane issues), tensor-memory owner
+//   warp 18    MMA issuer for dV and dK, bulk tensor stores of dS into dbias (converged, an elected lane issues)
+//   warp 19    TMA loads of the 16-bit bias tiles (converged, an elected lane issues)
 // A barrier operation answers after ~200 cycles on this GPU, so two issuers keep
 // the tensor pipe fed while the other one waits, and every role polls the
 // barriers it will need before it starts a stretch of independent work.
@@ -173,11 +173,14 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && live) {
-      tma_prefetch_desc(&p.map_q);
-      tma_prefetch_desc(&p.map_k);
-      tma_prefetch_desc(&p.map_v);
-      tma_prefetch_desc(&p.map_do);
+    // (whole warp converged, one elected lane issues)
+    if (live) {
+      if (lane == 0) {
+        tma_prefetch_desc(&p.map_q);
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
+        tma_prefetch_desc(&p.map_do);
+      }
       bool ok = true;
       constexpr int kBiasAhead = 1;  // bias tiles are pulled into L2 this many steps early
       uint32_t g = 0;                // steps issued so far, over all tiles
@@ -188,24 +191,30 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
         if (T_steps <= 0) continue;
         const int b = bh / p.H, h = bh - b * p.H, n0 = nb * 128;
         // K and V are single tiles: free once the previous tile's last S and dP are through
-        if (kvi >= 1) ok = mbar_wait(&kv_empty, (kvi - 1) & 1, ctx, kSiteKVEmpty, it);
+        if (kvi >= 1) ok = wait_warp(&kv_empty, (kvi - 1) & 1, ctx, kSiteKVEmpty, it);
         if (!ok) break;
         ++kvi;
-        mbar_expect_tx(&kv_full, 2 * L::kTile);
-        for (int kb = 0; kb < KB; ++kb) {
-          tma_load_4d(smem + L::kK + kb * kBlk, &p.map_k, &kv_full, kb * 64, h, n0, b);
-          tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
+        if (elect_one()) {
+          mbar_expect_tx(&kv_full, 2 * L::kTile);
+          for (int kb = 0; kb < KB; ++kb) {
+            tma_load_4d(smem + L::kK + kb * kBlk, &p.map_k, &kv_full, kb * 64, h, n0, b);
+            tma_load_4d(smem + L::kV + kb * kBlk, &p.map_v, &kv_full, kb * 64, h, n0, b);
+          }
         }
+        __syncwarp();
         // Bias tiles are pulled into L2 kBiasAhead steps before the row threads read them,
         // as one stream over tile boundaries: the last steps of a tile request the first
         // tiles of the next one (pf_done of them are out when that tile starts).
         auto bias_l2 = [&](int b_, int h_, int n0_, int mblk) {
           const int mp = mblk * 128;
           constexpr int kBox = BK == 1 ? 64 : (BK == 3 ? 32 : 128);  // keys per box of map_bias
+          if (elect_one()) {
 #pragma unroll
-          for (int c = 0; c < 128; c += kBox)
-            if (c == 0 || n0_ + c < p.N)
-              tma_prefetch_l2_4d(&p.map_bias, n0_ + c, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
+            for (int c = 0; c < 128; c += kBox)
+              if (c == 0 || n0_ + c < p.N)
+                tma_prefetch_l2_4d(&p.map_bias, n0_ + c, mp, h_ * p.bias_h_mul, b_ * p.bias_b_mul);
+          }
+          __syncwarp();
         };
         if (BIAS != 0) {
           for (int t = pf_done; t < kBiasAhead && t < T_steps; ++t) bias_l2(b, h, n0, i_start + t);
@@ -226,20 +235,26 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
               ++pf_done;
             }
           }
-          if (gs >= 2) ok = mbar_wait(&q_empty[qs], ((gs >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
+          if (gs >= 2) ok = wait_warp(&q_empty[qs], ((gs >> 1) - 1) & 1, ctx, kSiteQEmpty, t);
           if (!ok) break;
-          mbar_expect_tx(&q_full[qs], L::kTile);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kQ + qs * L::kTile + kb * kBlk, &p.map_q, &q_full[qs], kb * 64, h,
-                        m0, b);
+          if (elect_one()) {
+            mbar_expect_tx(&q_full[qs], L::kTile);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kQ + qs * L::kTile + kb * kBlk, &p.map_q, &q_full[qs], kb * 64, h,
+                          m0, b);
+          }
+          __syncwarp();
           const int ds = gs % kDoStages;
           const uint32_t du = gs / kDoStages;
-          if (du >= 1) ok = mbar_wait(&do_empty[ds], (du - 1) & 1, ctx, kSiteDoEmpty, t);
+          if (du >= 1) ok = wait_warp(&do_empty[ds], (du - 1) & 1, ctx, kSiteDoEmpty, t);
           if (!ok) break;
-          mbar_expect_tx(&do_full[ds], L::kTile);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kDo + ds * L::kTile + kb * kBlk, &p.map_do, &do_full[ds], kb * 64,
-                        h, m0, b);
+          if (elect_one()) {
+            mbar_expect_tx(&do_full[ds], L::kTile);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kDo + ds * L::kTile + kb * kBlk, &p.map_do, &do_full[ds], kb * 64,
+                          h, m0, b);
+          }
+          __syncwarp();
         }
         g += T_steps;
       }
@@ -555,8 +570,7 @@ __global__ void __launch_bounds__(640, 1) dkdv_kernel(const __grid_constant__ Dk
           f32x2 a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
           if (BK == 3)
             a = ffma2(f2(__uint_as_float(bcur.w[i]), __uint_as_float(bcur.w[i + 1])), f2(kLog2e, kLog2e), a);
-          // every fourth pair on the FMA pipe, the rest on the special-function unit
-          const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
+          const f32x2 pe = f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
           if (BK == 2) {
             const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
             pr[i] = (m2 & 0xFFu) != 0 ? f2_lo(pe) : 0.f;

@@ -306,8 +306,7 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
           } else {
             a = ffma2(f2(pr[i], pr[i + 1]), f2(p.scale_log2, p.scale_log2), f2(neg_lse, neg_lse));
           }
-          // every fourth pair on the FMA pipe, the rest on the special-function unit
-          const f32x2 pe = ((i & 6) == 2) ? ex2_poly2(a) : f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
+          const f32x2 pe = f2(ex2(f2_lo(a)), ex2(f2_hi(a)));
           if (BIAS == 2) {
             const uint32_t m2 = bcur.w[i >> 2] >> (8 * (i & 3));
             pr[i] = (m2 & 0xFFu) != 0 ? f2_lo(pe) : 0.f;

@@ -573,27 +573,6 @@ __device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
   return d;
 }
 
-// 2^x for a pair, on the FMA pipe instead of the special-function unit: round x to the
-// nearest integer n with the 1.5*2^23 trick, evaluate a degree-3 polynomial for 2^(x-n) on
-// [-0.5, 0.5] (relative error <= 1.5e-4, far below the rounding of a 16-bit result) and add n
-// to the exponent field.  x is clamped at -126, so a masked score (-inf) gives 1.2e-38
-// instead of exactly 0; results above 2^127 are not produced by the callers.  The
-// special-function unit delivers 4 results per cycle and scheduler; splitting the
-// exponentials of a tile between it and this routine shortens the exponential phase.
-__device__ __forceinline__ f32x2 ex2_poly2(f32x2 x) {
-  const f32x2 xc = f2(fmaxf(f2_lo(x), -126.f), fmaxf(f2_hi(x), -126.f));
-  const f32x2 t = fadd2(xc, f2(12582912.f, 12582912.f));          // low mantissa bits = n
-  const f32x2 n = fadd2(t, f2(-12582912.f, -12582912.f));
-  const f32x2 f = ffma2(n, f2(-1.f, -1.f), xc);                   // x - n
-  f32x2 p = ffma2(f, f2(0.0551716685f, 0.0551716685f), f2(0.242611125f, 0.242611125f));
-  p = ffma2(p, f, f2(0.693260968f, 0.693260968f));
-  p = ffma2(p, f, f2(0.999928057f, 0.999928057f));
-  uint32_t r0, r1;
-  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(r0) : "r"(__float_as_uint(f2_lo(t))), "r"(__float_as_uint(f2_lo(p))));
-  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(r1) : "r"(__float_as_uint(f2_hi(t))), "r"(__float_as_uint(f2_hi(p))));
-  return f2(__uint_as_float(r0), __uint_as_float(r1));
-}
-
 // 16-byte store to shared memory through a 32-bit shared-space address.
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w)

@@ -5,12 +5,12 @@
 // block they visit.  Roles (384 threads):
 //   warps 0-3   softmax group of tile 0: thread = one query row (= tensor-memory lane)
 //   warps 4-7   softmax group of tile 1
-//   warp 8      TMA producer (one lane): Q pair per unit, K ring (128-key stages), V ring
+//   warp 8      TMA producer (converged, an elected lane issues): Q pair per unit, K ring (128-key stages), V ring
 //               (64-key half stages)
-//   warp 9      MMA issuer of tile 0 (one lane), tensor-memory owner
-//   warp 10     TMA producer of the bias / mask ring (one lane); it also asks for the
+//   warp 9      MMA issuer of tile 0 (converged, an elected lane issues), tensor-memory owner
+//   warp 10     TMA producer of the bias / mask ring (converged, an elected lane issues); it also asks for the
 //               tiles a few units ahead to be pulled into L2
-//   warp 11     MMA issuer of tile 1 (one lane)
+//   warp 11     MMA issuer of tile 1 (converged, an elected lane issues)
 // Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  The 128 score columns of a tile are
 // two halves of 64 that swap roles every key block.  In step c (f = c & 1):
 //   columns [64f, 64f+64)       scores of keys 0-63, read first; afterwards they hold the
@@ -29,6 +29,12 @@
 //   the scores of keys 64-127 of block j+1 go over the columns P_t(j) was read from: same
 //   issuing thread, and products issued by one thread execute in issue order, so no barrier
 //   is needed between them
+// The control warps (producers, issuers) walk their loops with all 32 lanes converged and
+// elect a lane only for the TMA / MMA / commit instructions themselves: the descriptors and
+// coordinates are then warp-uniform values.  (Run by a single lane under a divergent branch,
+// every operand of every such instruction is first moved from that lane's registers, which
+// made a product of eight instructions take ~850 cycles to issue and a bias load reach the
+// ring a few hundred cycles later: 5-20 % of the kernel, depending on the workload.)
 // So a softmax group only waits for the tensor core at the start of a unit; the two tiles'
 // products interleave freely on the tensor core.  A row is owned by one thread: the row
 // maximum and the row sum need no exchange between threads.  The running maximum is only
@@ -286,7 +292,7 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
       }
     }
   } else if (warp == 9 || warp == 11) {
-    // ------------------------------------------- MMA issuer of tile slot t (one lane)
+    // ------------------------------------------- MMA issuer of tile slot t (converged, an elected lane issues)
     // (the whole warp walks the loop converged, one elected lane issues)
     if (live) {
       const int t = warp == 9 ? 0 : 1;
@@ -610,10 +616,9 @@ __global__ void __launch_bounds__(384, 1) fwd_kernel(const __grid_constant__ Fwd
             for (int i = 0; i < 32; i += 2) {
               const f32x2 a01 = ffma2(f2(s[2 * i], s[2 * i + 1]), mul2, negm2);
               const f32x2 a23 = ffma2(f2(s[2 * i + 2], s[2 * i + 3]), mul2, negm2);
-              // All exponentials on the special-function unit: with two row warps per scheduler it
-              // is busy under a third of the time, and the polynomial variant (FMA pipe) only adds
-              // instructions to warps that are latency bound (measured: 4 % slower with a quarter
-              // of the exponentials moved over).
+              // All exponentials on the special-function unit: a polynomial evaluated on the FMA
+              // pipe for part of them only adds instructions, and the row warps' time follows
+              // their instruction count (measured 2-4 % slower with an eighth to a quarter moved).
               const float p0 = ex2(f2_lo(a01)), p1 = ex2(f2_hi(a01));
               const float p2 = ex2(f2_lo(a23)), p3 = ex2(f2_hi(a23));
               sum01 = fadd2(sum01, f2(p0, p1));
