@@ -12,7 +12,8 @@
 // read through other descriptors, no data movement.
 // One CTA per (batch, head, block of 64 keys); it walks the 128-row query blocks that see
 // its keys.  Roles (192 threads): warps 0-3 row threads (thread = query row = tensor-memory
-// lane), warp 4 TMA producer, warp 5 MMA issuer and tensor-memory owner.  Shared memory:
+// lane), warp 4 TMA producer, warp 5 MMA issuer and tensor-memory owner (both run converged and elect
+// a lane for the issue).  Shared memory:
 // K 32 KB, V 32, Q 64, dO 64, P 16, dS 16 = 224 KB, everything single-staged: a step is
 //   loads of Q, dO -> S, dP -> row threads (P, dS) -> dV^T, dK^T -> next loads
 // without overlap between steps.  This is the correct-first version for a head dimension
@@ -78,7 +79,8 @@ __global__ void __launch_bounds__(192, 1) dkdv256_kernel(const __grid_constant__
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // the warp index as a value the compiler knows to be the same in all lanes
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   const int n0 = static_cast<int>(blockIdx.x) * 64;
   const int bh = blockIdx.y;
@@ -114,32 +116,40 @@ __global__ void __launch_bounds__(192, 1) dkdv256_kernel(const __grid_constant__
 
   if (warp == 4) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && live && steps > 0) {
-      tma_prefetch_desc(&p.map_q);
-      tma_prefetch_desc(&p.map_k);
-      tma_prefetch_desc(&p.map_v);
-      tma_prefetch_desc(&p.map_do);
-      mbar_expect_tx(&kv_full, 2 * kKTile256);
-      for (int kb = 0; kb < 4; ++kb) {
-        tma_load_4d(smem + kOffK + kb * kKBlk256, &p.map_k, &kv_full, kb * 64, h, n0, b);
-        tma_load_4d(smem + kOffV + kb * kKBlk256, &p.map_v, &kv_full, kb * 64, h, n0, b);
+    // (whole warp converged, one elected lane issues: the operands of the bulk loads and of
+    // the tensor-core instructions are then warp-uniform values)
+    if (live && steps > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&p.map_q);
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
+        tma_prefetch_desc(&p.map_do);
+        mbar_expect_tx(&kv_full, 2 * kKTile256);
+        for (int kb = 0; kb < 4; ++kb) {
+          tma_load_4d(smem + kOffK + kb * kKBlk256, &p.map_k, &kv_full, kb * 64, h, n0, b);
+          tma_load_4d(smem + kOffV + kb * kKBlk256, &p.map_v, &kv_full, kb * 64, h, n0, b);
+        }
       }
+      __syncwarp();
       bool ok = true;
       for (int s = 0; s < steps && ok; ++s) {
         // Q / dO (and the P / dS tiles) are free once the previous step's products are through
-        if (s >= 1) ok = mbar_wait(&qdo_empty, (s - 1) & 1, ctx, kSiteQdoEmpty, s);
+        if (s >= 1) ok = wait_warp(&qdo_empty, (s - 1) & 1, ctx, kSiteQdoEmpty, s);
         if (!ok) break;
         const int m0 = (i_start + s) * 128;
-        mbar_expect_tx(&qdo_full, 2 * kQTile256);
-        for (int kb = 0; kb < 4; ++kb) {
-          tma_load_4d(smem + kOffQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
-          tma_load_4d(smem + kOffDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
+        if (elect_one()) {
+          mbar_expect_tx(&qdo_full, 2 * kQTile256);
+          for (int kb = 0; kb < 4; ++kb) {
+            tma_load_4d(smem + kOffQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
+            tma_load_4d(smem + kOffDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
+          }
         }
+        __syncwarp();
       }
     }
   } else if (warp == 5) {
     // --------------------------------------------------------------- MMA issuer
-    if (lane == 0 && live && steps > 0) {
+    if (live && steps > 0) {
       constexpr bool bf = P2::kIsBf16;
       constexpr uint32_t idesc_s = make_idesc(bf, false, false, 128, 64);
       constexpr uint32_t idesc_t = make_idesc(bf, true, true, 128, 64);
@@ -147,30 +157,36 @@ __global__ void __launch_bounds__(192, 1) dkdv256_kernel(const __grid_constant__
       const uint32_t k_addr = smem_u32(smem + kOffK), v_addr = smem_u32(smem + kOffV);
       const uint64_t p_mn = make_sdesc(smem_u32(smem + kOffP), kBlk, 1024);
       const uint64_t ds_mn = make_sdesc(smem_u32(smem + kOffDs), kBlk, 1024);
-      bool ok = mbar_wait(&kv_full, 0, ctx, kSiteKV, 0);
+      bool ok = wait_warp(&kv_full, 0, ctx, kSiteKV, 0);
       for (int s = 0; s < steps && ok; ++s) {
-        ok = mbar_wait(&qdo_full, s & 1, ctx, kSiteQdoFull, s);
+        ok = wait_warp(&qdo_full, s & 1, ctx, kSiteQdoFull, s);
         if (!ok) break;
         tc_fence_after();
-        // S = Q K^T, dP = dO V^T: 16 K slices over four 64-column blocks
-        issue_gemm_ss<16, false, false>(tmem + kColS, make_sdesc(q_addr, 0, 1024), make_sdesc(k_addr, 0, 1024),
-                                        kBlk, kKBlk256, idesc_s, false);
-        issue_gemm_ss<16, false, false>(tmem + kColDp, make_sdesc(do_addr, 0, 1024), make_sdesc(v_addr, 0, 1024),
-                                        kBlk, kKBlk256, idesc_s, false);
-        mma_commit(&sdp_full);
-        ok = mbar_wait_hot(&pds_ready, s & 1, ctx, kSitePdsReady, s);
-        if (!ok) break;
-        tc_fence_after();
-        // dV^T[d half] += dO^T[d half] P,  dK^T[d half] += Q^T[d half] dS  (K = 128 query rows)
-        for (int hh = 0; hh < 2; ++hh) {
-          issue_gemm_ss<8, true, true>(tmem + kColDv + hh * 64, make_sdesc(do_addr + 2 * hh * kBlk, kBlk, 1024),
-                                       p_mn, kBlk, kBlk, idesc_t, s > 0);
-          issue_gemm_ss<8, true, true>(tmem + kColDk + hh * 64, make_sdesc(q_addr + 2 * hh * kBlk, kBlk, 1024),
-                                       ds_mn, kBlk, kBlk, idesc_t, s > 0);
+        if (elect_one()) {
+          // S = Q K^T, dP = dO V^T: 16 K slices over four 64-column blocks
+          issue_gemm_ss<16, false, false>(tmem + kColS, make_sdesc(q_addr, 0, 1024), make_sdesc(k_addr, 0, 1024),
+                                          kBlk, kKBlk256, idesc_s, false);
+          issue_gemm_ss<16, false, false>(tmem + kColDp, make_sdesc(do_addr, 0, 1024), make_sdesc(v_addr, 0, 1024),
+                                          kBlk, kKBlk256, idesc_s, false);
+          mma_commit(&sdp_full);
         }
-        mma_commit(&qdo_empty);
+        __syncwarp();
+        ok = wait_warp_hot(&pds_ready, s & 1, ctx, kSitePdsReady, s);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          // dV^T[d half] += dO^T[d half] P,  dK^T[d half] += Q^T[d half] dS  (K = 128 query rows)
+          for (int hh = 0; hh < 2; ++hh) {
+            issue_gemm_ss<8, true, true>(tmem + kColDv + hh * 64, make_sdesc(do_addr + 2 * hh * kBlk, kBlk, 1024),
+                                         p_mn, kBlk, kBlk, idesc_t, s > 0);
+            issue_gemm_ss<8, true, true>(tmem + kColDk + hh * 64, make_sdesc(q_addr + 2 * hh * kBlk, kBlk, 1024),
+                                         ds_mn, kBlk, kBlk, idesc_t, s > 0);
+          }
+          mma_commit(&qdo_empty);
+        }
+        __syncwarp();
       }
-      if (ok) mma_commit(&acc_done);
+      if (ok && elect_one()) mma_commit(&acc_done);
     }
     __syncwarp();
   } else {

@@ -139,40 +139,52 @@ __global__ void __launch_bounds__(608, 1) dq_recompute_kernel(const __grid_const
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && live) {
-      tma_prefetch_desc(&p.map_q);
-      tma_prefetch_desc(&p.map_k);
-      tma_prefetch_desc(&p.map_v);
-      tma_prefetch_desc(&p.map_do);
+    // (whole warp converged, one elected lane issues)
+    if (live) {
+      if (lane == 0) {
+        tma_prefetch_desc(&p.map_q);
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
+        tma_prefetch_desc(&p.map_do);
+      }
       bool ok = true;
       uint32_t gj = 0;  // key blocks issued so far, over all tiles
       int bh, m_block, nblk;
       for (int it = 0; ok && tile_at(it, bh, m_block, nblk); ++it) {
         const int b = bh / p.H, h = bh - b * p.H, m0 = m_block * 128;
         // Q and dO are single tiles: free once the previous tile's last S and dP are through
-        if (it >= 1) ok = mbar_wait(&qdo_empty, (it - 1) & 1, ctx, kSiteQdoEmpty, it);
+        if (it >= 1) ok = wait_warp(&qdo_empty, (it - 1) & 1, ctx, kSiteQdoEmpty, it);
         if (!ok) break;
-        mbar_expect_tx(&qdo_full, 2 * L::kTile);
-        for (int kb = 0; kb < KB; ++kb) {
-          tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
-          tma_load_4d(smem + L::kDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
+        if (elect_one()) {
+          mbar_expect_tx(&qdo_full, 2 * L::kTile);
+          for (int kb = 0; kb < KB; ++kb) {
+            tma_load_4d(smem + L::kQ + kb * kBlk, &p.map_q, &qdo_full, kb * 64, h, m0, b);
+            tma_load_4d(smem + L::kDo + kb * kBlk, &p.map_do, &qdo_full, kb * 64, h, m0, b);
+          }
         }
+        __syncwarp();
         for (int j = 0; j < nblk && ok; ++j) {
           const uint32_t g = gj + j;
           const int st = g & 1;
           const int n0 = j * 128;
-          if (g >= 2) ok = mbar_wait(&k_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
+          if (g >= 2) ok = wait_warp(&k_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteKEmpty, j);
           if (!ok) break;
-          mbar_expect_tx(&k_full[st], L::kTile);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
-                        n0, b);
-          if (g >= 2) ok = mbar_wait(&v_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
+          if (elect_one()) {
+            mbar_expect_tx(&k_full[st], L::kTile);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kK + st * L::kTile + kb * kBlk, &p.map_k, &k_full[st], kb * 64, h,
+                          n0, b);
+          }
+          __syncwarp();
+          if (g >= 2) ok = wait_warp(&v_empty[st], ((g >> 1) - 1) & 1, ctx, kSiteVEmpty, j);
           if (!ok) break;
-          mbar_expect_tx(&v_full[st], L::kTile);
-          for (int kb = 0; kb < KB; ++kb)
-            tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
-                        n0, b);
+          if (elect_one()) {
+            mbar_expect_tx(&v_full[st], L::kTile);
+            for (int kb = 0; kb < KB; ++kb)
+              tma_load_4d(smem + L::kV + st * L::kTile + kb * kBlk, &p.map_v, &v_full[st], kb * 64, h,
+                          n0, b);
+          }
+          __syncwarp();
         }
         gj += nblk;
       }
