@@ -8,11 +8,13 @@
 // epilogue.  Roles (640 threads):
 //   warps 0-15 "row" threads: warp w works on tensor-memory lanes 32*(w&3)..+31
 //              (query rows of the block) and on the 32-key column quarter (w>>2)
-//   warp 16    TMA producer (converged, an elected lane issues): K, V per tile; Q ring (2), dO ring; bias tiles
-//              are asked into L2 two steps ahead
-//   warp 17    MMA issuer for S and dP (converged, an elected lane issues), tensor-memory owner
-//   warp 18    MMA issuer for dV and dK, bulk tensor stores of dS into dbias (converged, an elected lane issues)
-//   warp 19    TMA loads of the 16-bit bias tiles (converged, an elected lane issues)
+//   warp 16    TMA producer: K, V per tile; Q ring (2), dO ring; bias tiles are asked
+//              into L2 one step ahead
+//   warp 17    MMA issuer for S and dP, tensor-memory owner
+//   warp 18    MMA issuer for dV and dK, bulk tensor stores of dS into dbias
+//   warp 19    TMA loads of the 16-bit bias tiles
+// The four control warps walk their loops with all lanes converged and elect a lane only
+// for the TMA / MMA / commit instructions, whose operands are then warp-uniform values.
 // A barrier operation answers after ~200 cycles on this GPU, so two issuers keep
 // the tensor pipe fed while the other one waits, and every role polls the
 // barriers it will need before it starts a stretch of independent work.
